@@ -1,0 +1,76 @@
+"""ctypes binding of ``libvsa_b200.so`` (declared in ``include/vsa_b200.h``).
+
+The library is built in-tree by ``python -m cudnn_vsa_b200.build``.  There is no fallback:
+if the shared object is missing or an entry point fails, a ``RuntimeError`` says so.
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_float, c_int32, c_int64, c_void_p
+from pathlib import Path
+
+import torch
+
+LIB_PATH = Path(__file__).resolve().parent / "lib" / "libvsa_b200.so"
+
+_P, _I32, _I64, _F = c_void_p, c_int32, c_int64, c_float
+
+# name -> (restype, argtypes); mirrors include/vsa_b200.h one to one.
+SIGNATURES = {
+    "vsa_abi_version": (_I32, []),
+    "vsa_row_gather": (_I32, [_P, _P, _P, _I64, _I64, _P]),
+    "vsa_row_scatter": (_I32, [_P, _P, _P, _I64, _I64, _P]),
+    "vsa_slots_pool": (_I32, [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I64, _I64, _I32, _P]),
+    "vsa_route_scratch_bytes": (_I64, [_I64, _I64, _I32]),
+    "vsa_route": (_I32, [_P, _P, _I32, _I32, _I32, _I32, _I32, _I32, _I32, _I32, _I32, _P, _I64, _I32, _P,
+                         _I64, _P]),
+    "vsa_fine_fwd": (_I32, [_P, _P, _P, _I64, _I64, _I32, _P, _P, _I64, _I64, _I32, _P, _F, _P, _P, _P, _P,
+                            _P, _P, _P, _I64, _P, _P]),
+    "vsa_merge_bwd": (_I32, [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I64, _I64, _I32, _P]),
+    "vsa_kv_mask_words": (_I64, [_I64]),
+    "vsa_fine_bwd": (_I32, [_P, _P, _P, _P, _I64, _I64, _I32, _P, _P, _I64, _I64, _I32, _P, _P, _F, _P, _P,
+                            _P, _P, _P, _P, _I64, _I64, _P, _P, _P, _P, _P, _I32, _P, _P, _P, _P, _P, _I32,
+                            _P, _P]),
+    "vsa_partition_indices": (_I32, [_P, _P, _P, _P, _P, _I64, _I32, _I32, _I32, _I32, _I64, _I64, _P]),
+    "vsa_merge_partial": (_I32, [_P, _P, _P, _P, _I64, _I32, _P]),
+}
+
+_STATUS = {1: "bad argument", 2: "CUDA error", 3: "cuTensorMapEncodeTiled unavailable",
+           4: "tensor map rejected", 5: "size beyond a documented limit"}
+
+_lib = None
+
+
+def load():
+    """Return the loaded library, raising if it was not built."""
+    global _lib
+    if _lib is None:
+        if not LIB_PATH.exists():
+            raise RuntimeError(
+                f"{LIB_PATH} is missing: build it with `python -m cudnn_vsa_b200.build` "
+                "(the VSA path has no fallback implementation)")
+        lib = ctypes.CDLL(str(LIB_PATH))
+        for name, (restype, argtypes) in SIGNATURES.items():
+            fn = getattr(lib, name)
+            fn.restype, fn.argtypes = restype, argtypes
+        _lib = lib
+    return _lib
+
+
+def ptr(tensor):
+    """Device address of a tensor (``None`` passes a null pointer)."""
+    return None if tensor is None else c_void_p(tensor.data_ptr())
+
+
+def stream():
+    return c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def call(name, *args):
+    """Invoke an int-returning entry point and raise on a nonzero status."""
+    rc = getattr(load(), name)(*args)
+    if rc != 0:
+        detail = _STATUS.get(rc, "unknown status")
+        if rc == 2:
+            detail += f" ({torch.cuda.get_device_name()}; check that the device is sm_100)"
+        raise RuntimeError(f"{name} failed with status {rc}: {detail}")

@@ -1,0 +1,204 @@
+// Shared device helpers for the sm_100a VSA kernels: status codes, bounded mbarrier waits,
+// TMA tile loads, tcgen05 (UMMA) descriptors, TMEM allocation and TMEM<->register moves.
+#pragma once
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace vsa {
+
+constexpr int kBlock = 64;   // slots per block
+constexpr int kDim = 128;    // head dimension
+
+// Status values returned by the C entry points (0 = success).
+enum Status : int {
+  kOk = 0,
+  kBadArgument = 1,     // null pointer, non-positive size, unsupported width
+  kCudaError = 2,       // a CUDA runtime call failed (cudaGetLastError has the cause)
+  kNoDriverEntry = 3,   // cuTensorMapEncodeTiled could not be resolved
+  kTensorMapError = 4,  // cuTensorMapEncodeTiled rejected the tensor
+  kTooLarge = 5,        // size beyond a documented limit
+};
+
+// Device-side error word values written through the caller's status pointer.
+enum DeviceError : int {
+  kDevOk = 0,
+  kDevWaitTimeout = 100,  // + a site id: a bounded mbarrier wait gave up
+};
+
+#define VSA_DEVICE __device__ __forceinline__
+
+VSA_DEVICE uint32_t smem_u32(const void* p) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+
+// ------------------------------------------------------------------------------------------
+// mbarrier
+VSA_DEVICE void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+VSA_DEVICE void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
+               : "memory");
+}
+VSA_DEVICE bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t done;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.b32 %0, 1, 0, p;\n\t}"
+      : "=r"(done)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return done != 0;
+}
+
+// Spin limit of every wait in these kernels, in SM clock cycles (about one second).
+constexpr long long kWaitCycles = 2000000000LL;
+
+// Bounded wait.  `abort_flag` lives in shared memory; once any wait of the CTA has timed out
+// every later wait returns at once, so the CTA drains its loops, frees TMEM and exits.
+VSA_DEVICE bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* status,
+                          int site) {
+  if (*abort_flag) return false;
+  if (mbar_try_wait(bar, parity)) return true;
+  const long long start = clock64();
+  while (!mbar_try_wait(bar, parity)) {
+    if (*abort_flag) return false;
+    if (clock64() - start > kWaitCycles) {
+      *abort_flag = 1;
+      if (status != nullptr) atomicCAS(status, 0, kDevWaitTimeout + site);
+      return false;
+    }
+  }
+  return true;
+}
+
+VSA_DEVICE void fence_barrier_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
+// Make generic-proxy shared-memory writes visible to the async proxy (TMA, tcgen05.mma).
+VSA_DEVICE void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+// ------------------------------------------------------------------------------------------
+// TMA: one 64-element x 64-row BF16 box of a [rows, heads, 128] tensor, 128-byte swizzled.
+VSA_DEVICE void tma_load_box(void* smem_dst, const CUtensorMap* map, uint64_t* bar, int d0, int head,
+                             int row0) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes "
+      "[%0], [%1, {%3, %4, %5}], [%2];"
+      ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(d0),
+      "r"(head), "r"(row0)
+      : "memory");
+}
+VSA_DEVICE void tma_prefetch_desc(const CUtensorMap* map) {
+  asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(map)) : "memory");
+}
+
+constexpr int kHalfTileBytes = kBlock * 64 * 2;  // 64 rows x 64 BF16 = 8 KiB (one swizzle-wide box)
+constexpr int kTileBytes = 2 * kHalfTileBytes;   // 64 rows x 128 BF16 = 16 KiB
+
+// Loads the 64x128 tile of block `block`, head `head` as two boxes: [d 0..63] then [d 64..127].
+VSA_DEVICE void tma_load_tile(void* smem_dst, const CUtensorMap* map, uint64_t* bar, int head, int block) {
+  tma_load_box(smem_dst, map, bar, 0, head, block * kBlock);
+  tma_load_box(static_cast<char*>(smem_dst) + kHalfTileBytes, map, bar, 64, head, block * kBlock);
+}
+
+// ------------------------------------------------------------------------------------------
+// tcgen05: tensor memory
+VSA_DEVICE void tmem_alloc(uint32_t* smem_result, uint32_t columns) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_result)),
+               "r"(columns)
+               : "memory");
+}
+VSA_DEVICE void tmem_relinquish() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+VSA_DEVICE void tmem_dealloc(uint32_t base, uint32_t columns) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(base), "r"(columns) : "memory");
+}
+VSA_DEVICE void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+VSA_DEVICE void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+VSA_DEVICE void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+VSA_DEVICE void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+// Arrive on an mbarrier once every tcgen05.mma issued so far by this thread has completed.
+VSA_DEVICE void umma_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
+               : "memory");
+}
+
+// Shared-memory matrix descriptor, 128-byte swizzle, descriptor version 1 (sm_100).
+//   K-major operand  (rows = M or N, 128 bytes of K per row): lbo unused, sbo = 1024 (8 rows).
+//   MN-major operand (rows = K, 128 bytes of M/N per row): lbo = bytes to the next 64 M/N elements,
+//                     sbo = 1024 (next 8 K rows).
+VSA_DEVICE uint64_t umma_smem_desc(uint32_t smem_addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+  uint64_t desc = 0;
+  desc |= static_cast<uint64_t>((smem_addr & 0x3FFFF) >> 4);
+  desc |= static_cast<uint64_t>((lbo_bytes >> 4) & 0x3FFF) << 16;
+  desc |= static_cast<uint64_t>((sbo_bytes >> 4) & 0x3FFF) << 32;
+  desc |= static_cast<uint64_t>(1) << 46;  // version
+  desc |= static_cast<uint64_t>(2) << 61;  // SWIZZLE_128B
+  return desc;
+}
+
+// Instruction descriptor: BF16 x BF16 -> FP32, dense, M x N, operand majors (0 = K, 1 = MN).
+__host__ __device__ constexpr uint32_t umma_idesc(int m, int n, int a_mn_major, int b_mn_major) {
+  return (1u << 4)                               // accumulator FP32
+         | (1u << 7) | (1u << 10)                // A, B = BF16
+         | (static_cast<uint32_t>(a_mn_major) << 15) | (static_cast<uint32_t>(b_mn_major) << 16)
+         | (static_cast<uint32_t>(n >> 3) << 17) | (static_cast<uint32_t>(m >> 4) << 24);
+}
+
+// D[tmem] (+)= A[smem] * B[smem]; one K=16 step.  Issued by a single thread.
+VSA_DEVICE void umma_ss(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
+// An M=64 accumulator occupies lanes 0..15 of each 32-lane TMEM quarter (row r at lane
+// 32*(r/16) + r%16).  The 16x32bx2 shape gives lane t%16 of the warp's quarter to thread t:
+// threads 0..15 read columns [col, col+N), threads 16..31 read [col+split, col+split+N).
+#define VSA_TMEM_LD_16x32bx2_X32(r, taddr, split)                                                     \
+  asm volatile(                                                                                       \
+      "tcgen05.ld.sync.aligned.16x32bx2.x32.b32 "                                                     \
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "                       \
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32], " #split ";" \
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),     \
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]),         \
+        "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]),      \
+        "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]),      \
+        "=r"(r[29]), "=r"(r[30]), "=r"(r[31])                                                           \
+      : "r"(taddr)                                                                                      \
+      : "memory")
+
+#define VSA_TMEM_ST_16x32bx2_X32(r, taddr, split)                                                     \
+  asm volatile(                                                                                       \
+      "tcgen05.st.sync.aligned.16x32bx2.x32.b32 [%0], " #split ", "                                   \
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "                      \
+      "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"              \
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]),        \
+      "r"(r[7]), "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]),       \
+      "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]),    \
+      "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]),    \
+      "r"(r[31])                                                                                        \
+      : "memory")
+
+// Byte offset of the 16-byte chunk `chunk` (0..7) of row `row` inside a 64-row x 128-byte
+// swizzle-128B tile: rows are 128 bytes apart and the chunk index is XORed with row % 8.
+VSA_DEVICE uint32_t swizzled_offset(int row, int chunk) {
+  return static_cast<uint32_t>(row * 128 + ((chunk ^ (row & 7)) << 4));
+}
+
+VSA_DEVICE uint32_t pack_bf16(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+VSA_DEVICE float2 unpack_bf16(uint32_t v) {
+  return __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&v));
+}
+
+}  // namespace vsa

@@ -1,0 +1,495 @@
+// Block-sparse fine attention, backward, for sm_100a: two tcgen05 kernels without atomics.
+//
+//   dQ kernel   one CTA per (query block, head), walks the block's KV list like the forward:
+//               S = Q K^T, dP = dO V^T, dS = P * (dP - delta) * scale, dQ += dS K.
+//   dK/dV kernel one CTA per (KV block, head), walks the query blocks that list this KV block
+//               (a per-call bitmask built by build_kv_mask_kernel):
+//               S^T = K Q^T, dP^T = V dO^T, dV += P^T dO, dK += dS^T Q.
+//
+// P is recomputed from the saved LSE (natural log), so no softmax state is carried.  The
+// epilogues add the gradient that reaches a row through its block's pooled mean and scatter
+// the rows straight to the caller's row order, skipping padding slots.  Together they replace
+// the reference's fine backward call and its slot-to-row gathers
+// (reference vsa_core.py:23-30, 42-47; vsa_kernels.py:86-96, 161-176 adjoint).
+#include "vsa_common.cuh"
+#include "vsa_kernels.h"
+
+namespace vsa {
+
+namespace {
+
+constexpr int kThreads = 128;
+constexpr float kLog2e = 1.4426950408889634f;
+
+VSA_DEVICE float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+// D[64 x 64] = A[64 x 128] B[64 x 128]^T, both K-major tiles made of two 64-wide halves.
+VSA_DEVICE void issue_nt_128(uint32_t tmem_d, const uint8_t* a, const uint8_t* b) {
+  constexpr uint32_t idesc = umma_idesc(64, 64, 0, 0);
+#pragma unroll
+  for (int ks = 0; ks < 8; ++ks) {
+    const uint32_t off = (ks >> 2) * kHalfTileBytes + (ks & 3) * 32;
+    umma_ss(tmem_d, umma_smem_desc(smem_u32(a) + off, 16, 1024), umma_smem_desc(smem_u32(b) + off, 16, 1024),
+            idesc, ks > 0);
+  }
+}
+
+// D[64 x 128] (+)= A[64 x 64] B[64 x 128]: A K-major (one 64-wide tile), B a row-major tile
+// read as MN-major (its rows are the K index).
+VSA_DEVICE void issue_nn_64(uint32_t tmem_d, const uint8_t* a, const uint8_t* b, bool accumulate) {
+  constexpr uint32_t idesc = umma_idesc(64, 128, 0, 1);
+#pragma unroll
+  for (int ks = 0; ks < 4; ++ks) {
+    umma_ss(tmem_d, umma_smem_desc(smem_u32(a) + ks * 32, 16, 1024),
+            umma_smem_desc(smem_u32(b) + ks * 2048, kHalfTileBytes, 1024), idesc, accumulate || ks > 0);
+  }
+}
+
+VSA_DEVICE void bulk_load(void* smem_dst, const void* gmem_src, uint32_t bytes, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+      ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(gmem_src)), "r"(bytes), "r"(smem_u32(bar))
+      : "memory");
+}
+
+// Pooled-mean gradient of `block` for this thread's 64 columns, already divided by the block size.
+VSA_DEVICE void load_pool_term(float (&term)[64], const void* pool, int pool_f32, const int32_t* block_coarse,
+                               int block, int size, long long width, long long col) {
+  long long prow = -1;
+  if (pool != nullptr) prow = pool_f32 ? block : (block_coarse != nullptr ? block_coarse[block] : -1);
+  if (prow < 0) {
+#pragma unroll
+    for (int i = 0; i < 64; ++i) term[i] = 0.f;
+    return;
+  }
+  const float inv = 1.f / static_cast<float>(size > 1 ? size : 1);
+  if (pool_f32) {
+    const float4* src = reinterpret_cast<const float4*>(static_cast<const float*>(pool) + prow * width + col);
+#pragma unroll
+    for (int c = 0; c < 16; ++c) {
+      const float4 f = __ldg(src + c);
+      term[4 * c] = f.x * inv, term[4 * c + 1] = f.y * inv, term[4 * c + 2] = f.z * inv, term[4 * c + 3] = f.w * inv;
+    }
+  } else {
+    const uint4* src = reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(pool) + prow * width + col);
+#pragma unroll
+    for (int c = 0; c < 8; ++c) {
+      const uint4 u = __ldg(src + c);
+      const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float2 f = unpack_bf16(w[e]);
+        term[8 * c + 2 * e] = f.x * inv, term[8 * c + 2 * e + 1] = f.y * inv;
+      }
+    }
+  }
+}
+
+// Reads this thread's 64 accumulator columns (or zeros), adds the pooled term and stores the row:
+// BF16 to `dst_row` when `write`, or FP32 into `f32_row` (added to its content when `accumulate`).
+VSA_DEVICE void store_grad_row(__nv_bfloat16* dst_row, bool have_acc, uint32_t tmem_addr, const float (&term)[64],
+                               bool write, float* f32_row, bool accumulate) {
+  float acc[64];
+#pragma unroll
+  for (int c = 0; c < 2; ++c) {
+    uint32_t bits[32] = {};
+    if (have_acc) {
+      VSA_TMEM_LD_16x32bx2_X32(bits, tmem_addr + c * 32, 64);
+      tmem_wait_ld();
+    }
+#pragma unroll
+    for (int i = 0; i < 32; ++i) acc[c * 32 + i] = __uint_as_float(bits[i]) + term[c * 32 + i];
+  }
+  if (f32_row != nullptr) {
+    float4* dst = reinterpret_cast<float4*>(f32_row);
+#pragma unroll
+    for (int c = 0; c < 16; ++c) {
+      float4 v = make_float4(acc[4 * c], acc[4 * c + 1], acc[4 * c + 2], acc[4 * c + 3]);
+      if (accumulate) {
+        const float4 old = dst[c];
+        v.x += old.x, v.y += old.y, v.z += old.z, v.w += old.w;
+      }
+      dst[c] = v;
+    }
+  } else if (write) {
+    uint4* dst = reinterpret_cast<uint4*>(dst_row);
+#pragma unroll
+    for (int c = 0; c < 8; ++c)
+      dst[c] = make_uint4(pack_bf16(acc[8 * c], acc[8 * c + 1]), pack_bf16(acc[8 * c + 2], acc[8 * c + 3]),
+                          pack_bf16(acc[8 * c + 4], acc[8 * c + 5]), pack_bf16(acc[8 * c + 6], acc[8 * c + 7]));
+  }
+}
+
+// ------------------------------------------------------------------------------------------ dQ
+constexpr int kDqTmemCols = 256;  // S [0,64)  dP [64,128)  dQ [128,256)
+
+struct __align__(1024) DqSmem {
+  uint8_t q[kTileBytes];
+  uint8_t d_o[kTileBytes];
+  uint8_t k[2][kTileBytes];
+  uint8_t v[2][kTileBytes];
+  uint8_t ds[kHalfTileBytes];
+  uint64_t qdo_full, kv_full[2], sp_done, dq_done;
+  uint32_t tmem_base;
+  int abort_flag;
+};
+
+}  // namespace
+
+__global__ void __launch_bounds__(kThreads) fine_bwd_dq_kernel(const __grid_constant__ FineBwdParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  DqSmem& sm = *reinterpret_cast<DqSmem*>(smem_raw + ((1024 - (smem_u32(smem_raw) & 1023)) & 1023));
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int qb = blockIdx.x, head = blockIdx.y;
+  const int row = warp * 16 + (lane & 15);
+  const int half = lane >> 4;
+  const int n = p.counts[static_cast<long long>(head) * p.count_head_stride + qb];
+  const int32_t* list = p.indices + static_cast<long long>(head) * p.index_head_stride +
+                        static_cast<long long>(qb) * p.capacity;
+
+  if (tid == 0) {
+    mbar_init(&sm.qdo_full, 1);
+    mbar_init(&sm.kv_full[0], 1);
+    mbar_init(&sm.kv_full[1], 1);
+    mbar_init(&sm.sp_done, 1);
+    mbar_init(&sm.dq_done, 1);
+    sm.abort_flag = 0;
+    fence_barrier_init();
+  }
+  if (warp == 0) {
+    tmem_alloc(&sm.tmem_base, kDqTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = sm.tmem_base;
+  const uint32_t lane_base = static_cast<uint32_t>(warp * 32) << 16;
+  volatile int* abort_flag = &sm.abort_flag;
+
+  if (tid == 0 && n > 0) {
+    mbar_expect_tx(&sm.qdo_full, 2 * kTileBytes);
+    tma_load_tile(sm.q, &p.q_map, &sm.qdo_full, head, qb);
+    tma_load_tile(sm.d_o, &p.do_map, &sm.qdo_full, head, qb);
+    for (int s = 0; s < 2 && s < n; ++s) {
+      mbar_expect_tx(&sm.kv_full[s], 2 * kTileBytes);
+      tma_load_tile(sm.k[s], &p.k_map, &sm.kv_full[s], head, list[s]);
+      tma_load_tile(sm.v[s], &p.v_map, &sm.kv_full[s], head, list[s]);
+    }
+    mbar_wait(&sm.qdo_full, 0, abort_flag, p.status, 11);
+    mbar_wait(&sm.kv_full[0], 0, abort_flag, p.status, 12);
+    tc_fence_after();
+    issue_nt_128(tmem, sm.q, sm.k[0]);
+    issue_nt_128(tmem + 64, sm.d_o, sm.v[0]);
+    umma_commit(&sm.sp_done);
+  }
+
+  const long long slot = static_cast<long long>(qb) * kBlock + row;
+  const float lse = p.lse[static_cast<long long>(head) * p.q_slots + slot];
+  const float delta = p.delta[static_cast<long long>(head) * p.q_slots + slot];
+  const float sl2 = p.scale * kLog2e;
+  const float lse2 = lse * kLog2e;
+  const bool row_live = lse != -INFINITY;
+
+  for (int j = 0; j < n; ++j) {
+    const int b = j & 1;
+    const int kv_block = list[j];
+    const int kv_size = p.kv_sizes != nullptr ? p.kv_sizes[kv_block] : kBlock;
+    mbar_wait(&sm.sp_done, j & 1, abort_flag, p.status, 13);
+    tc_fence_after();
+    uint32_t s_bits[32], dp_bits[32];
+    VSA_TMEM_LD_16x32bx2_X32(s_bits, tmem + lane_base, 32);
+    VSA_TMEM_LD_16x32bx2_X32(dp_bits, tmem + lane_base + 64, 32);
+    tmem_wait_ld();
+    uint32_t packed[16];
+#pragma unroll
+    for (int i = 0; i < 32; i += 2) {
+      float ds[2];
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        const bool live = row_live && (half * 32 + i + e < kv_size);
+        const float pr = live ? fast_exp2(__uint_as_float(s_bits[i + e]) * sl2 - lse2) : 0.f;
+        ds[e] = pr * (__uint_as_float(dp_bits[i + e]) - delta) * p.scale;
+      }
+      packed[i >> 1] = pack_bf16(ds[0], ds[1]);
+    }
+    if (j > 0) {
+      // dQ_{j-1} done: the dS buffer and K/V stage b^1 are free again.
+      mbar_wait(&sm.dq_done, (j - 1) & 1, abort_flag, p.status, 14);
+      tc_fence_after();
+      if (tid == 0 && j + 1 < n) {
+        mbar_expect_tx(&sm.kv_full[b ^ 1], 2 * kTileBytes);
+        tma_load_tile(sm.k[b ^ 1], &p.k_map, &sm.kv_full[b ^ 1], head, list[j + 1]);
+        tma_load_tile(sm.v[b ^ 1], &p.v_map, &sm.kv_full[b ^ 1], head, list[j + 1]);
+      }
+      __syncwarp();
+    }
+#pragma unroll
+    for (int c = 0; c < 4; ++c)
+      *reinterpret_cast<uint4*>(sm.ds + swizzled_offset(row, half * 4 + c)) =
+          make_uint4(packed[4 * c], packed[4 * c + 1], packed[4 * c + 2], packed[4 * c + 3]);
+    fence_proxy_async_smem();
+    tc_fence_before();
+    __syncthreads();
+    if (tid == 0) {
+      tc_fence_after();
+      issue_nn_64(tmem + 128, sm.ds, sm.k[b], j > 0);
+      umma_commit(&sm.dq_done);
+      if (j + 1 < n) {
+        mbar_wait(&sm.kv_full[b ^ 1], ((j + 1) >> 1) & 1, abort_flag, p.status, 15);
+        tc_fence_after();
+        issue_nt_128(tmem, sm.q, sm.k[b ^ 1]);
+        issue_nt_128(tmem + 64, sm.d_o, sm.v[b ^ 1]);
+        umma_commit(&sm.sp_done);
+      }
+    }
+    __syncwarp();
+  }
+
+  if (n > 0) {
+    mbar_wait(&sm.dq_done, (n - 1) & 1, abort_flag, p.status, 16);
+    tc_fence_after();
+  }
+  const long long width = static_cast<long long>(p.heads) * kDim;
+  const long long col = static_cast<long long>(head) * kDim + half * 64;
+  const long long out_row = p.q_slot_row != nullptr ? p.q_slot_row[slot] : slot;
+  const int q_size = p.q_sizes != nullptr ? p.q_sizes[qb] : kBlock;
+  float term[64];
+  load_pool_term(term, p.dq_pool, p.pool_f32, p.q_block_coarse, qb, q_size, width, col);
+  const bool write = out_row >= 0 && out_row < p.q_out_rows;
+  store_grad_row(p.dq + (write ? out_row : 0) * width + col, n > 0, tmem + lane_base + 128, term, write,
+                 p.dq_f32 != nullptr ? p.dq_f32 + slot * width + col : nullptr, p.f32_accumulate != 0);
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(tmem, kDqTmemCols);
+}
+
+// ------------------------------------------------------------------------------------------ dK, dV
+namespace {
+
+constexpr int kDkvTmemCols = 512;  // S^T [0,64)  dP^T [64,128)  dK [128,256)  dV [256,384)
+
+struct __align__(1024) DkvSmem {
+  uint8_t k[kTileBytes];
+  uint8_t v[kTileBytes];
+  uint8_t q[2][kTileBytes];
+  uint8_t d_o[2][kTileBytes];
+  uint8_t pt[kHalfTileBytes];
+  uint8_t dst[kHalfTileBytes];
+  float lse[2][kBlock];
+  float delta[2][kBlock];
+  uint64_t kv_full, qd_full[2], sp_done, dkv_done;
+  uint32_t tmem_base;
+  int abort_flag;
+};
+
+struct MaskCursor {
+  const uint32_t* words;
+  int count, word;
+  uint32_t bits;
+  VSA_DEVICE int next() {
+    while (bits == 0) {
+      if (++word >= count) return -1;
+      bits = words[word];
+    }
+    const int bit = __ffs(bits) - 1;
+    bits &= bits - 1;
+    return word * 32 + bit;
+  }
+};
+
+}  // namespace
+
+__global__ void __launch_bounds__(kThreads) fine_bwd_dkv_kernel(const __grid_constant__ FineBwdParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  DkvSmem& sm = *reinterpret_cast<DkvSmem*>(smem_raw + ((1024 - (smem_u32(smem_raw) & 1023)) & 1023));
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int kvb = blockIdx.x, head = blockIdx.y;
+  const int row = warp * 16 + (lane & 15);  // KV slot inside the block
+  const int half = lane >> 4;               // which 32 query columns / 64 output columns
+  const uint32_t* mask = p.kv_mask + (static_cast<long long>(head) * p.kv_blocks + kvb) * p.mask_words;
+  int n = 0;
+  for (int w = 0; w < p.mask_words; ++w) n += __popc(mask[w]);
+
+  if (tid == 0) {
+    mbar_init(&sm.kv_full, 1);
+    mbar_init(&sm.qd_full[0], 1);
+    mbar_init(&sm.qd_full[1], 1);
+    mbar_init(&sm.sp_done, 1);
+    mbar_init(&sm.dkv_done, 1);
+    sm.abort_flag = 0;
+    fence_barrier_init();
+  }
+  if (warp == 0) {
+    tmem_alloc(&sm.tmem_base, kDkvTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = sm.tmem_base;
+  const uint32_t lane_base = static_cast<uint32_t>(warp * 32) << 16;
+  volatile int* abort_flag = &sm.abort_flag;
+
+  MaskCursor cursor{mask, p.mask_words, 0, (tid == 0 && p.mask_words > 0) ? mask[0] : 0u};
+  auto load_stage = [&](int stage, int q_block) {
+    mbar_expect_tx(&sm.qd_full[stage], 2 * kTileBytes + 2 * kBlock * 4);
+    tma_load_tile(sm.q[stage], &p.q_map, &sm.qd_full[stage], head, q_block);
+    tma_load_tile(sm.d_o[stage], &p.do_map, &sm.qd_full[stage], head, q_block);
+    const long long off = static_cast<long long>(head) * p.q_slots + static_cast<long long>(q_block) * kBlock;
+    bulk_load(sm.lse[stage], p.lse + off, kBlock * 4, &sm.qd_full[stage]);
+    bulk_load(sm.delta[stage], p.delta + off, kBlock * 4, &sm.qd_full[stage]);
+  };
+  if (tid == 0 && n > 0) {
+    mbar_expect_tx(&sm.kv_full, 2 * kTileBytes);
+    tma_load_tile(sm.k, &p.k_map, &sm.kv_full, head, kvb);
+    tma_load_tile(sm.v, &p.v_map, &sm.kv_full, head, kvb);
+    for (int s = 0; s < 2 && s < n; ++s) load_stage(s, cursor.next());
+    mbar_wait(&sm.kv_full, 0, abort_flag, p.status, 21);
+    mbar_wait(&sm.qd_full[0], 0, abort_flag, p.status, 22);
+    tc_fence_after();
+    issue_nt_128(tmem, sm.k, sm.q[0]);
+    issue_nt_128(tmem + 64, sm.v, sm.d_o[0]);
+    umma_commit(&sm.sp_done);
+  }
+
+  const int kv_size = p.kv_sizes != nullptr ? p.kv_sizes[kvb] : kBlock;
+  const bool key_live = row < kv_size;
+  const float sl2 = p.scale * kLog2e;
+
+  for (int j = 0; j < n; ++j) {
+    const int b = j & 1;
+    mbar_wait(&sm.sp_done, j & 1, abort_flag, p.status, 23);
+    // Every thread observes the stage's own barrier before reading the LSE / delta rows that
+    // the bulk copies wrote.
+    mbar_wait(&sm.qd_full[b], (j >> 1) & 1, abort_flag, p.status, 24);
+    tc_fence_after();
+    uint32_t s_bits[32], dp_bits[32];
+    VSA_TMEM_LD_16x32bx2_X32(s_bits, tmem + lane_base, 32);
+    VSA_TMEM_LD_16x32bx2_X32(dp_bits, tmem + lane_base + 64, 32);
+    tmem_wait_ld();
+    uint32_t p_packed[16], ds_packed[16];
+#pragma unroll
+    for (int i = 0; i < 32; i += 2) {
+      float pr[2], ds[2];
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        const int c = half * 32 + i + e;
+        const float lse = sm.lse[b][c];
+        const bool live = key_live && lse != -INFINITY;
+        pr[e] = live ? fast_exp2(__uint_as_float(s_bits[i + e]) * sl2 - lse * kLog2e) : 0.f;
+        ds[e] = pr[e] * (__uint_as_float(dp_bits[i + e]) - sm.delta[b][c]) * p.scale;
+      }
+      p_packed[i >> 1] = pack_bf16(pr[0], pr[1]);
+      ds_packed[i >> 1] = pack_bf16(ds[0], ds[1]);
+    }
+    if (j > 0) {
+      // dK/dV step j-1 done: P^T / dS^T buffers and Q/dO stage b^1 are free again.
+      mbar_wait(&sm.dkv_done, (j - 1) & 1, abort_flag, p.status, 25);
+      tc_fence_after();
+      if (tid == 0 && j + 1 < n) load_stage(b ^ 1, cursor.next());
+      __syncwarp();
+    }
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      const uint32_t off = swizzled_offset(row, half * 4 + c);
+      *reinterpret_cast<uint4*>(sm.pt + off) =
+          make_uint4(p_packed[4 * c], p_packed[4 * c + 1], p_packed[4 * c + 2], p_packed[4 * c + 3]);
+      *reinterpret_cast<uint4*>(sm.dst + off) =
+          make_uint4(ds_packed[4 * c], ds_packed[4 * c + 1], ds_packed[4 * c + 2], ds_packed[4 * c + 3]);
+    }
+    fence_proxy_async_smem();
+    tc_fence_before();
+    __syncthreads();
+    if (tid == 0) {
+      tc_fence_after();
+      issue_nn_64(tmem + 256, sm.pt, sm.d_o[b], j > 0);  // dV += P^T dO
+      issue_nn_64(tmem + 128, sm.dst, sm.q[b], j > 0);   // dK += dS^T Q
+      umma_commit(&sm.dkv_done);
+      if (j + 1 < n) {
+        mbar_wait(&sm.qd_full[b ^ 1], ((j + 1) >> 1) & 1, abort_flag, p.status, 26);
+        tc_fence_after();
+        issue_nt_128(tmem, sm.k, sm.q[b ^ 1]);
+        issue_nt_128(tmem + 64, sm.v, sm.d_o[b ^ 1]);
+        umma_commit(&sm.sp_done);
+      }
+    }
+    __syncwarp();
+  }
+
+  if (n > 0) {
+    mbar_wait(&sm.dkv_done, (n - 1) & 1, abort_flag, p.status, 27);
+    tc_fence_after();
+  }
+  const long long slot = static_cast<long long>(kvb) * kBlock + row;
+  const long long width = static_cast<long long>(p.heads) * kDim;
+  const long long col = static_cast<long long>(head) * kDim + half * 64;
+  const long long out_row = p.kv_slot_row != nullptr ? p.kv_slot_row[slot] : slot;
+  const bool write = out_row >= 0 && out_row < p.kv_out_rows;
+  float term[64];
+  load_pool_term(term, p.dk_pool, p.pool_f32, p.kv_block_coarse, kvb, kv_size, width, col);
+  store_grad_row(p.dk + (write ? out_row : 0) * width + col, n > 0, tmem + lane_base + 128, term, write,
+                 p.dk_f32 != nullptr ? p.dk_f32 + slot * width + col : nullptr, p.f32_accumulate != 0);
+  load_pool_term(term, p.dv_pool, p.pool_f32, p.kv_block_coarse, kvb, kv_size, width, col);
+  store_grad_row(p.dv + (write ? out_row : 0) * width + col, n > 0, tmem + lane_base + 256, term, write,
+                 p.dv_f32 != nullptr ? p.dv_f32 + slot * width + col : nullptr, p.f32_accumulate != 0);
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(tmem, kDkvTmemCols);
+}
+
+// Marks, for every (head, KV block), the query blocks whose list contains it.
+__global__ void build_kv_mask_kernel(const int32_t* indices, const int32_t* counts, long long index_head_stride,
+                                     long long count_head_stride, int capacity, int q_blocks, int kv_blocks,
+                                     uint32_t* mask, int mask_words) {
+  const int qb = blockIdx.x, head = blockIdx.y;
+  const int n = counts[static_cast<long long>(head) * count_head_stride + qb];
+  const int32_t* list = indices + static_cast<long long>(head) * index_head_stride +
+                        static_cast<long long>(qb) * capacity;
+  uint32_t* head_mask = mask + static_cast<long long>(head) * kv_blocks * mask_words;
+  for (int j = threadIdx.x; j < n; j += blockDim.x) {
+    const int kv = list[j];
+    if (kv >= 0 && kv < kv_blocks)
+      atomicOr(head_mask + static_cast<long long>(kv) * mask_words + (qb >> 5), 1u << (qb & 31));
+  }
+}
+
+cudaError_t launch_build_kv_mask(const int32_t* indices, const int32_t* counts, long long index_head_stride,
+                                 long long count_head_stride, int capacity, int heads, int q_blocks,
+                                 int kv_blocks, uint32_t* mask, int mask_words, cudaStream_t stream) {
+  const size_t bytes = static_cast<size_t>(heads) * kv_blocks * mask_words * sizeof(uint32_t);
+  cudaError_t err = cudaMemsetAsync(mask, 0, bytes, stream);
+  if (err != cudaSuccess) return err;
+  dim3 grid(q_blocks, heads);
+  build_kv_mask_kernel<<<grid, 128, 0, stream>>>(indices, counts, index_head_stride, count_head_stride, capacity,
+                                                 q_blocks, kv_blocks, mask, mask_words);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_fine_bwd_dq(const FineBwdParams& params, cudaStream_t stream) {
+  const size_t smem = sizeof(DqSmem) + 1024;
+  cudaError_t err = cudaFuncSetAttribute(fine_bwd_dq_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         static_cast<int>(smem));
+  if (err != cudaSuccess) return err;
+  dim3 grid(params.q_blocks, params.heads);
+  fine_bwd_dq_kernel<<<grid, kThreads, smem, stream>>>(params);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_fine_bwd_dkv(const FineBwdParams& params, cudaStream_t stream) {
+  // 512 TMEM columns per CTA: ask for more than half of the SM's shared memory so that two CTAs
+  // can never be resident together and wait on each other's tensor memory.
+  const size_t smem = sizeof(DkvSmem) + 1024 > 120 * 1024 ? sizeof(DkvSmem) + 1024 : 120 * 1024;
+  cudaError_t err = cudaFuncSetAttribute(fine_bwd_dkv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         static_cast<int>(smem));
+  if (err != cudaSuccess) return err;
+  dim3 grid(params.kv_blocks, params.heads);
+  fine_bwd_dkv_kernel<<<grid, kThreads, smem, stream>>>(params);
+  return cudaGetLastError();
+}
+
+}  // namespace vsa

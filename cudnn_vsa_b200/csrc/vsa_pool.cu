@@ -1,0 +1,184 @@
+// HBM-bound block kernels: one CTA per 64-slot block, one thread per 16-byte column chunk.
+//
+//   slots_pool   reads Q, K, V rows once through the slot map, writes the zero-padded slot
+//                tensors and the FP32 block means (sum of the slots / max(size, 1)) plus their
+//                BF16 rounding placed at the block's row of the coarse streams.  Fuses the
+//                reference's three slot gathers with its pooling reduction
+//                (vsa_kernels.py:66-83, 119-158, 161-188; vsa.py:96-104).
+//   merge_bwd    adjoint of `out = fine + gate * coarse[block]` fused with the gather of dO into
+//                slots and with delta = rowsum(dO * O_fine) that the fine backward needs
+//                (vsa_kernels.py:204-246; vsa_core.py:23-30 consumes O and dO).
+#include "vsa_common.cuh"
+#include "vsa_kernels.h"
+
+namespace vsa {
+
+namespace {
+
+constexpr int kChunk = 8;  // BF16 elements per 16-byte chunk
+
+VSA_DEVICE void accumulate(float (&acc)[8], const uint4& v) {
+  const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+  for (int e = 0; e < 4; ++e) {
+    const float2 f = unpack_bf16(w[e]);
+    acc[2 * e] += f.x;
+    acc[2 * e + 1] += f.y;
+  }
+}
+
+__global__ void slots_pool_kernel(const PoolParams p) {
+  __shared__ long long rows[kBlock];
+  const long long block = blockIdx.x;
+  if (threadIdx.x < kBlock) {
+    const long long slot = block * kBlock + threadIdx.x;
+    rows[threadIdx.x] = p.slot_row != nullptr ? p.slot_row[slot] : slot;
+  }
+  __syncthreads();
+  const int chunks = p.width / kChunk;
+  const int size = p.sizes[block];
+  const float inv = 1.f / static_cast<float>(size > 1 ? size : 1);
+  const long long coarse_row = (p.block_coarse != nullptr && p.mean_bf16 != nullptr) ? p.block_coarse[block] : -1;
+  const uint4* src[3] = {reinterpret_cast<const uint4*>(p.q), reinterpret_cast<const uint4*>(p.k),
+                         reinterpret_cast<const uint4*>(p.v)};
+  uint4* dst[3] = {reinterpret_cast<uint4*>(p.q_slots), reinterpret_cast<uint4*>(p.k_slots),
+                   reinterpret_cast<uint4*>(p.v_slots)};
+  for (int c = threadIdx.x; c < chunks; c += blockDim.x) {
+    float acc[3][8] = {};
+#pragma unroll 4
+    for (int s = 0; s < kBlock; ++s) {
+      const long long row = rows[s];
+      const long long out = (block * kBlock + s) * chunks + c;
+#pragma unroll
+      for (int t = 0; t < 3; ++t) {
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (row >= 0) v = __ldg(src[t] + row * chunks + c);
+        if (dst[t] != nullptr) dst[t][out] = v;
+        accumulate(acc[t], v);
+      }
+    }
+#pragma unroll
+    for (int t = 0; t < 3; ++t) {
+      float mean[8];
+#pragma unroll
+      for (int e = 0; e < 8; ++e) mean[e] = acc[t][e] * inv;
+      if (p.mean_f32 != nullptr) {
+        float4* m = reinterpret_cast<float4*>(p.mean_f32 + (t * p.blocks + block) * p.width + c * kChunk);
+        m[0] = make_float4(mean[0], mean[1], mean[2], mean[3]);
+        m[1] = make_float4(mean[4], mean[5], mean[6], mean[7]);
+      }
+      if (coarse_row >= 0) {
+        uint4* m = reinterpret_cast<uint4*>(p.mean_bf16 + (t * p.coarse_rows + coarse_row) * p.width + c * kChunk);
+        *m = make_uint4(pack_bf16(mean[0], mean[1]), pack_bf16(mean[2], mean[3]), pack_bf16(mean[4], mean[5]),
+                        pack_bf16(mean[6], mean[7]));
+      }
+    }
+  }
+}
+
+// Sum over the 16 consecutive lanes that hold one head's 128 columns.
+VSA_DEVICE float head_sum(float x) {
+#pragma unroll
+  for (int off = 8; off > 0; off >>= 1) x += __shfl_xor_sync(0xffffffffu, x, off);
+  return x;
+}
+
+__global__ void merge_bwd_kernel(const MergeBwdParams p) {
+  __shared__ long long rows[kBlock];
+  const long long block = blockIdx.x;
+  if (threadIdx.x < kBlock) {
+    const long long slot = block * kBlock + threadIdx.x;
+    rows[threadIdx.x] = p.slot_row != nullptr ? p.slot_row[slot] : slot;
+  }
+  __syncthreads();
+  const int width = p.heads * kDim;
+  const int chunks = width / kChunk;
+  const long long slots = p.blocks * kBlock;
+  const long long coarse_row = (p.block_coarse != nullptr && p.coarse != nullptr) ? p.block_coarse[block] : -1;
+  const uint4* grad = reinterpret_cast<const uint4*>(p.grad);
+  const uint4* gate = reinterpret_cast<const uint4*>(p.gate);
+  const uint4* fine = reinterpret_cast<const uint4*>(p.o_slots);
+  // blockDim is a multiple of 32 and chunks a multiple of 16, so whole 16-lane groups stay together.
+  for (int c0 = 0; c0 < chunks; c0 += blockDim.x) {
+    const int c = c0 + threadIdx.x;
+    const bool active = c < chunks;
+    const int head = active ? (c * kChunk) / kDim : 0;
+    float cz[8] = {};
+    if (active && coarse_row >= 0) {
+      const uint4 v = __ldg(reinterpret_cast<const uint4*>(p.coarse) + coarse_row * chunks + c);
+      float z[8] = {};
+      accumulate(z, v);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) cz[e] = z[e];
+    }
+    float dc[8] = {};
+    for (int s = 0; s < kBlock; ++s) {
+      const long long row = rows[s];
+      const long long slot = block * kBlock + s;
+      float g[8] = {}, o[8] = {};
+      uint4 gv = make_uint4(0, 0, 0, 0);
+      if (active && row >= 0) {
+        gv = __ldg(grad + row * chunks + c);
+        accumulate(g, gv);
+        accumulate(o, __ldg(fine + slot * chunks + c));
+        if (coarse_row >= 0) {
+          float gt[8] = {};
+          accumulate(gt, __ldg(gate + row * chunks + c));
+          float dg[8];
+#pragma unroll
+          for (int e = 0; e < 8; ++e) {
+            dg[e] = g[e] * cz[e];
+            dc[e] += g[e] * gt[e];
+          }
+          if (p.dgate != nullptr)
+            reinterpret_cast<uint4*>(p.dgate)[row * chunks + c] =
+                make_uint4(pack_bf16(dg[0], dg[1]), pack_bf16(dg[2], dg[3]), pack_bf16(dg[4], dg[5]),
+                           pack_bf16(dg[6], dg[7]));
+        } else if (p.dgate != nullptr) {
+          reinterpret_cast<uint4*>(p.dgate)[row * chunks + c] = make_uint4(0, 0, 0, 0);
+        }
+      }
+      if (active && p.grad_slots != nullptr) reinterpret_cast<uint4*>(p.grad_slots)[slot * chunks + c] = gv;
+      float part = 0.f;
+#pragma unroll
+      for (int e = 0; e < 8; ++e) part += g[e] * o[e];
+      part = head_sum(part);
+      if (active && (threadIdx.x & 15) == 0) p.delta[head * slots + slot] = part;
+    }
+    if (coarse_row >= 0 && p.dcoarse != nullptr) {
+      const uint4 packed = make_uint4(pack_bf16(dc[0], dc[1]), pack_bf16(dc[2], dc[3]), pack_bf16(dc[4], dc[5]),
+                                      pack_bf16(dc[6], dc[7]));
+      if (active) reinterpret_cast<uint4*>(p.dcoarse)[coarse_row * chunks + c] = packed;
+      float rounded[8] = {};
+      accumulate(rounded, packed);
+      float part = 0.f;
+#pragma unroll
+      for (int e = 0; e < 8; ++e) part += rounded[e] * cz[e];
+      part = head_sum(part);
+      if (active && p.coarse_delta != nullptr && (threadIdx.x & 15) == 0)
+        p.coarse_delta[head * p.coarse_rows + coarse_row] = part;
+    }
+  }
+}
+
+int block_threads(int chunks) {
+  int threads = ((chunks + 31) / 32) * 32;
+  return threads > 512 ? 512 : threads;
+}
+
+}  // namespace
+
+cudaError_t launch_slots_pool(const PoolParams& params, cudaStream_t stream) {
+  if (params.blocks == 0) return cudaSuccess;
+  slots_pool_kernel<<<static_cast<unsigned>(params.blocks), block_threads(params.width / kChunk), 0, stream>>>(params);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_merge_bwd(const MergeBwdParams& params, cudaStream_t stream) {
+  if (params.blocks == 0) return cudaSuccess;
+  merge_bwd_kernel<<<static_cast<unsigned>(params.blocks), block_threads(params.heads * kDim / kChunk), 0, stream>>>(
+      params);
+  return cudaGetLastError();
+}
+
+}  // namespace vsa

@@ -1,0 +1,139 @@
+/* C ABI of libvsa_b200.so: the sm_100a kernels behind the packed video-sparse-attention path.
+ *
+ * Conventions
+ *   - Every pointer is a device pointer unless stated; the library never allocates, frees or
+ *     synchronises, keeps no mutable global state, and launches on the stream it is given
+ *     (`stream` is a cudaStream_t passed as void*).  The caller allocates every output and
+ *     every scratch buffer (sizes below).
+ *   - Activations are BF16, row-major `[rows, heads, 128]`; a "slot" tensor holds `blocks * 64`
+ *     rows (64 zero-padded slots per block).  `width = heads * 128`.
+ *   - Return value: 0 on success, otherwise a VSA_STATUS_* code (a CUDA launch error leaves the
+ *     cause in cudaGetLastError).  `status` arguments point to one int32 in device memory that a
+ *     kernel sets to 100 + site if one of its bounded waits gave up; the host checks it after the
+ *     step and may pass null.
+ *   - Each entry point names the reference interface it replaces (file:line in the reference
+ *     project).  The reference itself has no native code: these are the calls a maintainer binds
+ *     with ctypes in place of the Triton kernels, the cuDNN block-sparse call and the FA4 call.
+ */
+#ifndef VSA_B200_H_
+#define VSA_B200_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define VSA_STATUS_OK 0
+#define VSA_STATUS_BAD_ARGUMENT 1
+#define VSA_STATUS_CUDA_ERROR 2
+#define VSA_STATUS_NO_DRIVER_ENTRY 3
+#define VSA_STATUS_TENSOR_MAP 4
+#define VSA_STATUS_TOO_LARGE 5
+
+/* Library version, bumped when a signature changes. */
+int vsa_abi_version(void);
+
+/* out[i, :] = map[i] >= 0 ? x[map[i], :] : 0 for `out_rows` rows of `row_bytes` bytes.
+ * Replaces vsa_kernels.py:66-83 (`gather`, slot padding / restore and their adjoints) and the
+ * forward direction of vsa_kernels.py:11-42 (`reorder_tokens`). */
+int vsa_row_gather(const void* x, const int64_t* map, void* out, int64_t out_rows, int64_t row_bytes, void* stream);
+
+/* out[rows[i], :] = x[i, :] for `in_rows` unique rows; `out` rows that are not listed keep their
+ * content (the caller zero-fills it when the listed rows are a shard).
+ * Replaces the inverse direction of vsa_kernels.py:11-42. */
+int vsa_row_scatter(const void* x, const int64_t* rows, void* out, int64_t in_rows, int64_t row_bytes, void* stream);
+
+/* Q, K, V rows -> zero-padded slot tensors + FP32 block means (+ BF16 means placed at the
+ * block's row of the coarse streams).  `slot_row` null: inputs already are the slots.  Any of
+ * `*_slots`, `mean_f32`, `mean_bf16` may be null to skip that output.
+ * mean_f32: [3, blocks, width]; mean_bf16: [3, coarse_rows, width] (caller zero-fills it).
+ * Replaces vsa_kernels.py:99-101, 119-158 (Q/K/V slot gather) and :161-188 (block means). */
+int vsa_slots_pool(const void* q, const void* k, const void* v, const int64_t* slot_row, const int32_t* block_sizes,
+                   void* q_slots, void* k_slots, void* v_slots, float* mean_f32, const int32_t* block_coarse,
+                   void* mean_bf16, int64_t coarse_rows, int64_t blocks, int32_t heads, void* stream);
+
+/* Bytes of `scratch` that vsa_route needs for a region of `rows` query blocks x `region` KV
+ * blocks when it may process `heads` heads at once (it processes fewer per pass if given less). */
+int64_t vsa_route_scratch_bytes(int64_t rows, int64_t region, int32_t heads);
+
+/* Top-`keep` selection for one video region: for query blocks [q_begin, q_end) and every head,
+ * writes the `keep` KV blocks of [kv_first, kv_last) with the highest FP32 scores
+ * q_mean[b + q_mean_offset] . k_mean[j + k_mean_offset], ascending, into
+ * indices[head][b][cursor .. cursor + keep).  q_mean / k_mean: FP32 [*, heads, 128].
+ * Replaces vsa_core.py:61-72 (`_route_group`: SGEMM + topk + sort). */
+int vsa_route(const float* q_mean, const float* k_mean, int32_t heads, int32_t q_begin, int32_t q_end,
+              int32_t q_mean_offset, int32_t kv_first, int32_t kv_last, int32_t k_mean_offset, int32_t keep,
+              int32_t cursor, int32_t* indices, int64_t index_head_stride, int32_t capacity, void* scratch,
+              int64_t scratch_bytes, void* stream);
+
+/* Block-sparse attention forward over 64-slot blocks (tcgen05 + TMA).
+ *   q [q_blocks*64, heads, 128], k / v [kv_blocks*64, heads, 128] BF16 slot tensors;
+ *   indices [heads, q_blocks, capacity] (head stride 0 = one table for all heads), counts alike;
+ *   kv_sizes [kv_blocks] valid slots per KV block or null.
+ *   o_slots [q_blocks*64, heads, 128] BF16 and lse [heads, q_blocks*64] FP32 (natural log, -inf for
+ *   an empty list) are always written.
+ *   If `out` is non-null the merged result fine + gate * coarse[block_coarse[block]] is also
+ *   written to row slot_row[slot] of out [out_rows, heads, 128] (slot_row null = identity,
+ *   block_coarse null or -1 = fine only, gate of such rows is never read).
+ * Replaces vsa_core.py:15-20, 33-40 (cuDNN BSA forward), vsa_core.py:87-97 (FA4 coarse, when
+ * called on the pooled block tokens), vsa_kernels.py:191-201 and vsa.py:111-117 (restore + merge). */
+int vsa_fine_fwd(const void* q, const void* k, const void* v, int64_t q_blocks, int64_t kv_blocks, int32_t heads,
+                 const int32_t* indices, const int32_t* counts, int64_t index_head_stride, int64_t count_head_stride,
+                 int32_t capacity, const int32_t* kv_sizes, float scale, void* o_slots, float* lse,
+                 const int64_t* slot_row, const int32_t* block_coarse, const void* gate, const void* coarse,
+                 void* out, int64_t out_rows, int32_t* status, void* stream);
+
+/* Adjoint of the gate merge fused with the slot gather of dO and with delta = rowsum(dO * O_fine).
+ *   grad [rows, width] BF16 in caller order -> grad_slots [blocks*64, width] (null: not wanted),
+ *   dgate [rows, width], dcoarse [coarse_rows, width], delta [heads, blocks*64] FP32,
+ *   coarse_delta [heads, coarse_rows] FP32 = rowsum(dcoarse * coarse).
+ * gate / coarse / block_coarse / dgate / dcoarse / coarse_delta are null for packs without coarse.
+ * Replaces vsa_kernels.py:204-246 (`_fine_coarse_gate_add_dgate/_dcoarse`) and the dO slot gather. */
+int vsa_merge_bwd(const void* grad, const void* gate, const void* coarse, const void* o_slots, const int64_t* slot_row,
+                  const int32_t* block_coarse, void* grad_slots, void* dgate, void* dcoarse, float* delta,
+                  float* coarse_delta, int64_t blocks, int64_t coarse_rows, int32_t heads, void* stream);
+
+/* Words per (head, KV block) row of the query-block bitmask used by vsa_fine_bwd. */
+int64_t vsa_kv_mask_words(int64_t q_blocks);
+
+/* Block-sparse attention backward (two tcgen05 kernels, no atomics).
+ *   d_o: dO in slot order; lse from the forward; delta = rowsum(dO * O).
+ *   kv_mask: scratch of heads * kv_blocks * vsa_kv_mask_words(q_blocks) uint32, rebuilt each call.
+ *   BF16 outputs dq [q_out_rows, width], dk / dv [kv_out_rows, width] receive row slot_row[slot]
+ *   (null map = identity; padding slots are skipped), plus pool[block] / max(size, 1) when a
+ *   pooled-mean gradient is given: pool_f32 = 0 -> BF16 rows indexed by *_block_coarse[block],
+ *   pool_f32 = 1 -> FP32 rows indexed by block.
+ *   If dq_f32 / dk_f32 / dv_f32 are non-null the results go to those FP32 slot-order buffers
+ *   instead (added to their content when f32_accumulate != 0) - the ring path's running dQ and
+ *   travelling dK / dV (vsa_kernels.py:356-372).
+ * Replaces vsa_core.py:23-30, 42-47 (cuDNN BSA backward), the FA4 backward of the coarse call,
+ * the pooling adjoint of vsa_kernels.py:161-176 and the slot->row gathers of :86-96. */
+int vsa_fine_bwd(const void* q, const void* k, const void* v, const void* d_o, int64_t q_blocks, int64_t kv_blocks,
+                 int32_t heads, const int32_t* indices, const int32_t* counts, int64_t index_head_stride,
+                 int64_t count_head_stride, int32_t capacity, const int32_t* q_sizes, const int32_t* kv_sizes,
+                 float scale, const float* lse, const float* delta, uint32_t* kv_mask, void* dq, void* dk, void* dv,
+                 int64_t q_out_rows, int64_t kv_out_rows, const int64_t* q_slot_row, const int64_t* kv_slot_row,
+                 const void* dq_pool, const void* dk_pool, const void* dv_pool, int32_t pool_f32,
+                 const int32_t* q_block_coarse, const int32_t* kv_block_coarse, float* dq_f32, float* dk_f32,
+                 float* dv_f32, int32_t f32_accumulate, int32_t* status, void* stream);
+
+/* Ring: split routing rows into per-owner lists of owner-local block ids.
+ *   index [rows, capacity], counts [rows], global_to_gather [global blocks] int64.
+ *   out_lists [ring_size][list_stride] holds rows of `out_capacity` ids, out_counts
+ *   [ring_size][count_stride].  Replaces vsa_kernels.py:285-353 (`partition_indices`). */
+int vsa_partition_indices(const int32_t* index, const int32_t* counts, const int64_t* global_to_gather,
+                          int32_t* out_lists, int32_t* out_counts, int64_t rows, int32_t capacity,
+                          int32_t out_capacity, int32_t ring_size, int32_t peer_blocks, int64_t list_stride,
+                          int64_t count_stride, void* stream);
+
+/* Ring: merge one step's normalised partial output (BF16 [slots, heads, 128]) and LSE
+ * ([heads, slots]) into the running FP32 output and LSE, in place.
+ * Replaces vsa_kernels.py:375-397 (`_merge_partial`). */
+int vsa_merge_partial(float* out, float* lse, const void* part, const float* part_lse, int64_t slots, int32_t heads,
+                      void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* VSA_B200_H_ */
