@@ -30,9 +30,9 @@ VSA_DEVICE void accumulate(float (&acc)[8], const uint4& v) {
 __global__ void slots_pool_kernel(const PoolParams p) {
   __shared__ long long rows[kBlock];
   const long long block = blockIdx.x;
-  if (threadIdx.x < kBlock) {
-    const long long slot = block * kBlock + threadIdx.x;
-    rows[threadIdx.x] = p.slot_row != nullptr ? p.slot_row[slot] : slot;
+  for (int i = threadIdx.x; i < kBlock; i += blockDim.x) {
+    const long long slot = block * kBlock + i;
+    rows[i] = p.slot_row != nullptr ? p.slot_row[slot] : slot;
   }
   __syncthreads();
   const int chunks = p.width / kChunk;
@@ -86,9 +86,9 @@ VSA_DEVICE float head_sum(float x) {
 __global__ void merge_bwd_kernel(const MergeBwdParams p) {
   __shared__ long long rows[kBlock];
   const long long block = blockIdx.x;
-  if (threadIdx.x < kBlock) {
-    const long long slot = block * kBlock + threadIdx.x;
-    rows[threadIdx.x] = p.slot_row != nullptr ? p.slot_row[slot] : slot;
+  for (int i = threadIdx.x; i < kBlock; i += blockDim.x) {
+    const long long slot = block * kBlock + i;
+    rows[i] = p.slot_row != nullptr ? p.slot_row[slot] : slot;
   }
   __syncthreads();
   const int width = p.heads * kDim;

@@ -159,8 +159,8 @@ def fine_attention(q, k, v, indices, counts, sizes, scale):
     """
     slots, heads, dim = q.shape
     blocks = slots // BLOCK
-    qf, kf, vf = (x.float().view(blocks, BLOCK, heads, dim) for x in (q, k, v))
-    size_of = (torch.full((blocks,), BLOCK, dtype=torch.int64) if sizes is None
+    qf, kf, vf = (x.float().view(-1, BLOCK, heads, dim) for x in (q, k, v))
+    size_of = (torch.full((kf.shape[0],), BLOCK, dtype=torch.int64) if sizes is None
                else sizes.to(torch.int64))
     slot_ids = torch.arange(BLOCK)
     outs = [[None] * blocks for _ in range(heads)]

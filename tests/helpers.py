@@ -48,14 +48,18 @@ def from_bits(array):
 
 
 def assert_close(actual, expected, what, max_abs=MAX_ABS, rel_l2=REL_L2):
+    """max-abs and relative-L2 bounds.  The max-abs bound is taken relative to the reference's
+    peak magnitude when that exceeds one: a BF16 result cannot be closer than half an ulp
+    (0.016 at magnitude 4, 0.031 at 8), and gradients summed over many rows reach that size."""
     a, b = actual.detach().double().cpu().flatten(), expected.detach().double().cpu().flatten()
     assert a.shape == b.shape, (what, a.shape, b.shape)
     if not a.numel():
         return
     assert torch.isfinite(a).all(), f"{what}: non-finite values"
     err = (a - b).abs().max().item()
+    bound = max_abs * max(1.0, b.abs().max().item())
     rel = ((a - b).square().sum() / b.square().sum().clamp_min(1e-30)).sqrt().item()
-    assert err <= max_abs and rel <= rel_l2, f"{what}: max_abs={err:.3e} rel_l2={rel:.3e}"
+    assert err <= bound and rel <= rel_l2, f"{what}: max_abs={err:.3e} (bound {bound:.3e}) rel_l2={rel:.3e}"
 
 
 def routing_mismatches_are_near_ties(got, want, scores_list, counts, rel=1e-4):
