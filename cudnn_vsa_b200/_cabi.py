@@ -30,7 +30,7 @@ SIGNATURES = {
     "vsa_kv_mask_words": (_I64, [_I64]),
     "vsa_fine_bwd": (_I32, [_P, _P, _P, _P, _I64, _I64, _I32, _P, _P, _I64, _I64, _I32, _P, _P, _F, _P, _P,
                             _P, _P, _P, _P, _I64, _I64, _P, _P, _P, _P, _P, _I32, _P, _P, _P, _P, _P, _I32,
-                            _P, _P]),
+                            _I32, _P, _P]),
     "vsa_partition_indices": (_I32, [_P, _P, _P, _P, _P, _I64, _I32, _I32, _I32, _I32, _I64, _I64, _P]),
     "vsa_merge_partial": (_I32, [_P, _P, _P, _P, _I64, _I32, _P]),
 }
@@ -39,6 +39,9 @@ _STATUS = {1: "bad argument", 2: "CUDA error", 3: "cuTensorMapEncodeTiled unavai
            4: "tensor map rejected", 5: "size beyond a documented limit"}
 
 _lib = None
+
+# Kernels launched by this process through `call` (the benchmark reports the count per step).
+LAUNCHES = 0
 
 
 def load():
@@ -66,9 +69,14 @@ def stream():
     return c_void_p(torch.cuda.current_stream().cuda_stream)
 
 
-def call(name, *args):
-    """Invoke an int-returning entry point and raise on a nonzero status."""
+def call(name, *args, launches=1):
+    """Invoke an int-returning entry point and raise on a nonzero status.
+
+    ``launches`` is the number of kernels the call enqueues (one for most entry points).
+    """
+    global LAUNCHES
     rc = getattr(load(), name)(*args)
+    LAUNCHES += launches
     if rc != 0:
         detail = _STATUS.get(rc, "unknown status")
         if rc == 2:

@@ -190,13 +190,13 @@ int vsa_fine_bwd(const void* q, const void* k, const void* v, const void* d_o, i
                  int64_t q_out_rows, int64_t kv_out_rows, const int64_t* q_slot_row, const int64_t* kv_slot_row,
                  const void* dq_pool, const void* dk_pool, const void* dv_pool, int32_t pool_f32,
                  const int32_t* q_block_coarse, const int32_t* kv_block_coarse, float* dq_f32, float* dk_f32,
-                 float* dv_f32, int32_t f32_accumulate, int32_t* status, void* stream) {
+                 float* dv_f32, int32_t f32_accumulate, int32_t parts, int32_t* status, void* stream) {
   if (q == nullptr || k == nullptr || v == nullptr || d_o == nullptr || indices == nullptr || counts == nullptr ||
       lse == nullptr || delta == nullptr || kv_mask == nullptr || q_blocks <= 0 || kv_blocks <= 0 || heads <= 0 ||
       capacity <= 0)
     return vsa::kBadArgument;
-  if ((dq == nullptr && dq_f32 == nullptr) || (dk == nullptr && dk_f32 == nullptr) ||
-      (dv == nullptr && dv_f32 == nullptr))
+  if (((parts & 2) && dq == nullptr && dq_f32 == nullptr) ||
+      ((parts & 4) && ((dk == nullptr && dk_f32 == nullptr) || (dv == nullptr && dv_f32 == nullptr))))
     return vsa::kBadArgument;
   if (q_blocks > 0x7fffffffLL / vsa::kBlock || kv_blocks > 0x7fffffffLL / vsa::kBlock || heads > 65535)
     return vsa::kTooLarge;
@@ -244,10 +244,12 @@ int vsa_fine_bwd(const void* q, const void* k, const void* v, const void* d_o, i
   p.scale = scale;
   p.status = status;
   cudaStream_t s = as_stream(stream);
-  cudaError_t err = vsa::launch_build_kv_mask(indices, counts, index_head_stride, count_head_stride, capacity, heads,
-                                              p.q_blocks, p.kv_blocks, kv_mask, p.mask_words, s);
-  if (err == cudaSuccess) err = vsa::launch_fine_bwd_dq(p, s);
-  if (err == cudaSuccess) err = vsa::launch_fine_bwd_dkv(p, s);
+  cudaError_t err = cudaSuccess;
+  if (parts & 1)
+    err = vsa::launch_build_kv_mask(indices, counts, index_head_stride, count_head_stride, capacity, heads,
+                                    p.q_blocks, p.kv_blocks, kv_mask, p.mask_words, s);
+  if (err == cudaSuccess && (parts & 2)) err = vsa::launch_fine_bwd_dq(p, s);
+  if (err == cudaSuccess && (parts & 4)) err = vsa::launch_fine_bwd_dkv(p, s);
   return from_cuda(err);
 }
 

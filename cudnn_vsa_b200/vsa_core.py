@@ -144,10 +144,18 @@ def route(q_mean, k_mean, layout, plan=None):
     scratch = torch.empty(max(per_head, min(need, ROUTE_SCRATCH_BYTES)), dtype=torch.uint8,
                           device=index.device)
     for q_begin, q_end, kv_first, kv_last, keep, cursor in plan.spans:
+        per_head = max(1, (q_end - q_begin) * (kv_last - kv_first) * 4)
+        passes = -(-heads // max(1, min(heads, scratch.numel() // per_head)))
         _cabi.call("vsa_route", _p(q_mean), _p(k_mean), heads, q_begin, q_end, 0, kv_first, kv_last, 0,
                    keep, cursor, _p(index), index.stride(1), cap, _p(scratch), scratch.numel(),
-                   _cabi.stream())
+                   _cabi.stream(), launches=2 * passes)
+    plan.last_index = index
     return index
+
+
+def last_routing(layout):
+    """Routing table of the most recent forward pass of this layout (for FLOP accounting)."""
+    return getattr(device_plan(layout), "last_index", layout.routing_indices)
 
 
 def _fine_fwd(q, k, v, index, counts, head_strides, kv_sizes, scale, status, *, merge=None):
@@ -185,7 +193,7 @@ def _fine_bwd(q, k, v, d_o, index, counts, head_strides, q_sizes, kv_sizes, scal
                head_strides[0], head_strides[1], index.shape[-1], _p(q_sizes), _p(kv_sizes), scale, _p(lse),
                _p(delta), _p(mask), _p(dq), _p(dk), _p(dv), q_rows, kv_rows, _p(q_slot_row), _p(kv_slot_row),
                _p(dq_pool), _p(dk_pool), _p(dv_pool), 0, _p(q_block_coarse), _p(kv_block_coarse), None, None,
-               None, 0, _p(status), _cabi.stream())
+               None, 0, 7, _p(status), _cabi.stream(), launches=3)
     return dq, dk, dv
 
 

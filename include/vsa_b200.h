@@ -107,6 +107,8 @@ int64_t vsa_kv_mask_words(int64_t q_blocks);
  *   If dq_f32 / dk_f32 / dv_f32 are non-null the results go to those FP32 slot-order buffers
  *   instead (added to their content when f32_accumulate != 0) - the ring path's running dQ and
  *   travelling dK / dV (vsa_kernels.py:356-372).
+ *   `parts` selects what runs: bit 0 rebuilds kv_mask, bit 1 the dQ kernel, bit 2 the dK/dV
+ *   kernel (7 = everything; the pieces can be launched and timed one by one).
  * Replaces vsa_core.py:23-30, 42-47 (cuDNN BSA backward), the FA4 backward of the coarse call,
  * the pooling adjoint of vsa_kernels.py:161-176 and the slot->row gathers of :86-96. */
 int vsa_fine_bwd(const void* q, const void* k, const void* v, const void* d_o, int64_t q_blocks, int64_t kv_blocks,
@@ -116,7 +118,7 @@ int vsa_fine_bwd(const void* q, const void* k, const void* v, const void* d_o, i
                  int64_t q_out_rows, int64_t kv_out_rows, const int64_t* q_slot_row, const int64_t* kv_slot_row,
                  const void* dq_pool, const void* dk_pool, const void* dv_pool, int32_t pool_f32,
                  const int32_t* q_block_coarse, const int32_t* kv_block_coarse, float* dq_f32, float* dk_f32,
-                 float* dv_f32, int32_t f32_accumulate, int32_t* status, void* stream);
+                 float* dv_f32, int32_t f32_accumulate, int32_t parts, int32_t* status, void* stream);
 
 /* Ring: split routing rows into per-owner lists of owner-local block ids.
  *   index [rows, capacity], counts [rows], global_to_gather [global blocks] int64.
