@@ -46,6 +46,7 @@ WORKLOADS = {
                                 [S("video", (1, 45, 80)), S("text", 2048)],
                                 [S("video", (1, 45, 80)), S("text", 2048)]], 24, "raster"),
     "720p_single_sample_h12": ([[S("video", (31, 45, 80), .9), S("text", 2048)]], 12, "raster"),
+    "720p_single_sample_h6": ([[S("video", (31, 45, 80), .9), S("text", 2048)]], 6, "raster"),
     "ring_61x90x160_h24": ([[S("video", (61, 90, 160), .95), S("text", 4096)]], 24, "block"),
     "small_8x16x16_h2": ([[S("video", (8, 16, 16), .75), S("text", 256)]], 2, "raster"),
 }
