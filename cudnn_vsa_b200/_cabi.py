@@ -24,6 +24,7 @@ SIGNATURES = {
     "vsa_route_scratch_bytes": (_I64, [_I64, _I64, _I32]),
     "vsa_route": (_I32, [_P, _P, _I32, _I32, _I32, _I32, _I32, _I32, _I32, _I32, _I32, _P, _I64, _I32, _P,
                          _I64, _P]),
+    "vsa_route_static": (_I32, [_P, _P, _I32, _I32, _I32, _I32, _I32, _I32, _I32, _I32, _I32, _P, _I64, _I32, _P]),
     "vsa_fine_fwd": (_I32, [_P, _P, _P, _I64, _I64, _I32, _P, _P, _I64, _I64, _I32, _P, _F, _P, _P, _P, _P,
                             _P, _P, _P, _I64, _P, _P]),
     "vsa_merge_bwd": (_I32, [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I64, _I64, _I32, _P]),
@@ -36,7 +37,8 @@ SIGNATURES = {
 }
 
 _STATUS = {1: "bad argument", 2: "CUDA error", 3: "cuTensorMapEncodeTiled unavailable",
-           4: "tensor map rejected", 5: "size beyond a documented limit"}
+           4: "tensor map rejected", 5: "size beyond a documented limit",
+           6: "the request does not fit the library's 16 MiB built-in scratch array"}
 
 _lib = None
 

@@ -30,6 +30,7 @@ extern "C" {
 #define VSA_STATUS_NO_DRIVER_ENTRY 3
 #define VSA_STATUS_TENSOR_MAP 4
 #define VSA_STATUS_TOO_LARGE 5
+#define VSA_STATUS_STATIC_SCRATCH 6 /* request does not fit the library's built-in scratch array */
 
 /* Library version, bumped when a signature changes. */
 int vsa_abi_version(void);
@@ -66,6 +67,22 @@ int vsa_route(const float* q_mean, const float* k_mean, int32_t heads, int32_t q
               int32_t q_mean_offset, int32_t kv_first, int32_t kv_last, int32_t k_mean_offset, int32_t keep,
               int32_t cursor, int32_t* indices, int64_t index_head_stride, int32_t capacity, void* scratch,
               int64_t scratch_bytes, void* stream);
+
+/* vsa_route without a scratch argument, for callers that may not allocate device memory (a
+ * runtime plugin whose enqueue hook must not allocate, a process whose device memory belongs to
+ * another framework's pool).  No counterpart in the reference, which allocates freely through
+ * PyTorch.  The score matrix lives in a 16 MiB array inside the library's device image (held by
+ * every GPU that loads the library, from load to exit).  One head's scores,
+ * (q_end - q_begin) * (kv_last - kv_first) * 4 bytes, must fit in it, otherwise the call returns
+ * VSA_STATUS_STATIC_SCRATCH and does nothing; heads beyond what fits run in further passes.
+ * The call allocates and frees nothing.  All calls on a device share the array (it keeps the
+ * last call's contents; nothing in it needs clearing because each call writes every score it
+ * reads), so calls that overlap on the GPU race - keep them on one stream.  The first call on a
+ * device queries the array's address on the host; make it before any stream capture begins.
+ * Results are identical to vsa_route. */
+int vsa_route_static(const float* q_mean, const float* k_mean, int32_t heads, int32_t q_begin, int32_t q_end,
+                     int32_t q_mean_offset, int32_t kv_first, int32_t kv_last, int32_t k_mean_offset, int32_t keep,
+                     int32_t cursor, int32_t* indices, int64_t index_head_stride, int32_t capacity, void* stream);
 
 /* Block-sparse attention forward over 64-slot blocks (tcgen05 + TMA).
  *   q [q_blocks*64, heads, 128], k / v [kv_blocks*64, heads, 128] BF16 slot tensors;
