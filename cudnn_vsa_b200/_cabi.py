@@ -34,6 +34,8 @@ SIGNATURES = {
                             _I32, _P, _P]),
     "vsa_partition_indices": (_I32, [_P, _P, _P, _P, _P, _I64, _I32, _I32, _I32, _I32, _I64, _I64, _P]),
     "vsa_merge_partial": (_I32, [_P, _P, _P, _P, _I64, _I32, _P]),
+    "vsa_gate_merge": (_I32, [_P, _P, _P, _P, _P, _P, _P, _I64, _I32, _I64, _P]),
+    "vsa_grad_finish": (_I32, [_P, _P, _P, _I32, _P, _P, _P, _I64, _I32, _I64, _P]),
 }
 
 _STATUS = {1: "bad argument", 2: "CUDA error", 3: "cuTensorMapEncodeTiled unavailable",

@@ -273,4 +273,24 @@ int vsa_merge_partial(float* out, float* lse, const void* part, const float* par
                                              as_stream(stream)));
 }
 
+int vsa_gate_merge(const float* fine, const int64_t* slot_row, const int32_t* block_coarse, const void* gate,
+                   const void* coarse, void* o_slots, void* out, int64_t blocks, int32_t heads, int64_t out_rows,
+                   void* stream) {
+  if (fine == nullptr || out == nullptr || blocks < 0 || heads <= 0) return vsa::kBadArgument;
+  if (coarse != nullptr && (gate == nullptr || block_coarse == nullptr)) return vsa::kBadArgument;
+  return from_cuda(vsa::launch_gate_merge(fine, slot_row, block_coarse, static_cast<const __nv_bfloat16*>(gate),
+                                          static_cast<const __nv_bfloat16*>(coarse),
+                                          static_cast<__nv_bfloat16*>(o_slots), static_cast<__nv_bfloat16*>(out),
+                                          blocks, heads, out_rows, as_stream(stream)));
+}
+
+int vsa_grad_finish(const float* acc, const int64_t* slot_row, const void* pool, int32_t pool_f32,
+                    const int32_t* block_map, const int32_t* block_sizes, void* out, int64_t blocks, int32_t heads,
+                    int64_t out_rows, void* stream) {
+  if (acc == nullptr || out == nullptr || blocks < 0 || heads <= 0) return vsa::kBadArgument;
+  return from_cuda(vsa::launch_grad_finish(acc, slot_row, pool, pool_f32, block_map, block_sizes,
+                                           static_cast<__nv_bfloat16*>(out), blocks, heads, out_rows,
+                                           as_stream(stream)));
+}
+
 }  // extern "C"

@@ -137,6 +137,13 @@ struct MergeBwdParams {
 cudaError_t launch_merge_bwd(const MergeBwdParams& params, cudaStream_t stream);
 
 // ---------------------------------------------------------------------------- ring helpers
+cudaError_t launch_gate_merge(const float* fine, const int64_t* slot_row, const int32_t* block_coarse,
+                              const __nv_bfloat16* gate, const __nv_bfloat16* coarse, __nv_bfloat16* o_slots,
+                              __nv_bfloat16* out, long long blocks, int heads, long long out_rows,
+                              cudaStream_t stream);
+cudaError_t launch_grad_finish(const float* acc, const int64_t* slot_row, const void* pool, int pool_f32,
+                               const int32_t* block_map, const int32_t* sizes, __nv_bfloat16* out, long long blocks,
+                               int heads, long long out_rows, cudaStream_t stream);
 cudaError_t launch_partition_indices(const int32_t* index, const int32_t* counts, const int64_t* global_to_gather,
                                      int32_t* out_lists, int32_t* out_counts, long long rows, int capacity,
                                      int out_capacity, int ring_size, int peer_blocks, long long list_stride,

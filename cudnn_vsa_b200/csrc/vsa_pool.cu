@@ -161,6 +161,79 @@ __global__ void merge_bwd_kernel(const MergeBwdParams p) {
   }
 }
 
+// Ring epilogue of the forward pass: FP32 fine output in slot order -> BF16 copy for the backward
+// pass and the merged result `fine + gate * coarse[block]` in the caller's row order.
+__global__ void gate_merge_kernel(const float* __restrict__ fine, const int64_t* __restrict__ slot_row,
+                                  const int32_t* __restrict__ block_coarse, const __nv_bfloat16* __restrict__ gate,
+                                  const __nv_bfloat16* __restrict__ coarse, __nv_bfloat16* __restrict__ o_slots,
+                                  __nv_bfloat16* __restrict__ out, int width, long long out_rows) {
+  const long long block = blockIdx.x;
+  const int chunks = width / kChunk;
+  const long long coarse_row = (block_coarse != nullptr && coarse != nullptr) ? block_coarse[block] : -1;
+  for (int c = threadIdx.x; c < chunks; c += blockDim.x) {
+    float cz[8] = {};
+    if (coarse_row >= 0) accumulate(cz, __ldg(reinterpret_cast<const uint4*>(coarse) + coarse_row * chunks + c));
+    for (int s = 0; s < kBlock; ++s) {
+      const long long slot = block * kBlock + s;
+      const float4* src = reinterpret_cast<const float4*>(fine + slot * width + c * kChunk);
+      const float4 a = src[0], b = src[1];
+      float f[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+      if (o_slots != nullptr)
+        reinterpret_cast<uint4*>(o_slots)[slot * chunks + c] =
+            make_uint4(pack_bf16(f[0], f[1]), pack_bf16(f[2], f[3]), pack_bf16(f[4], f[5]), pack_bf16(f[6], f[7]));
+      const long long row = slot_row != nullptr ? slot_row[slot] : slot;
+      if (row < 0 || row >= out_rows) continue;
+      if (coarse_row >= 0) {
+        float g[8] = {};
+        accumulate(g, __ldg(reinterpret_cast<const uint4*>(gate) + row * chunks + c));
+#pragma unroll
+        for (int e = 0; e < 8; ++e) f[e] = __fadd_rn(f[e], __fmul_rn(g[e], cz[e]));
+      }
+      reinterpret_cast<uint4*>(out)[row * chunks + c] =
+          make_uint4(pack_bf16(f[0], f[1]), pack_bf16(f[2], f[3]), pack_bf16(f[4], f[5]), pack_bf16(f[6], f[7]));
+    }
+  }
+}
+
+// Ring epilogue of the backward pass: FP32 slot-order gradient + pooled-mean term -> BF16 rows.
+__global__ void grad_finish_kernel(const float* __restrict__ acc, const int64_t* __restrict__ slot_row,
+                                   const void* __restrict__ pool, int pool_f32, const int32_t* __restrict__ block_map,
+                                   const int32_t* __restrict__ sizes, __nv_bfloat16* __restrict__ out, int width,
+                                   long long out_rows) {
+  const long long block = blockIdx.x;
+  const int chunks = width / kChunk;
+  long long prow = -1;
+  if (pool != nullptr) prow = pool_f32 ? block : (block_map != nullptr ? block_map[block] : -1);
+  const int size = sizes != nullptr ? sizes[block] : kBlock;
+  const float inv = 1.f / static_cast<float>(size > 1 ? size : 1);
+  for (int c = threadIdx.x; c < chunks; c += blockDim.x) {
+    float term[8] = {};
+    if (prow >= 0) {
+      if (pool_f32) {
+        const float4* src = reinterpret_cast<const float4*>(static_cast<const float*>(pool) + prow * width + c * kChunk);
+        const float4 a = src[0], b = src[1];
+        term[0] = a.x, term[1] = a.y, term[2] = a.z, term[3] = a.w, term[4] = b.x, term[5] = b.y, term[6] = b.z,
+        term[7] = b.w;
+      } else {
+        accumulate(term, __ldg(reinterpret_cast<const uint4*>(pool) + prow * chunks + c));
+      }
+#pragma unroll
+      for (int e = 0; e < 8; ++e) term[e] *= inv;
+    }
+    for (int s = 0; s < kBlock; ++s) {
+      const long long slot = block * kBlock + s;
+      const long long row = slot_row != nullptr ? slot_row[slot] : slot;
+      if (row < 0 || row >= out_rows) continue;
+      const float4* src = reinterpret_cast<const float4*>(acc + slot * width + c * kChunk);
+      const float4 a = src[0], b = src[1];
+      const float f[8] = {a.x + term[0], a.y + term[1], a.z + term[2], a.w + term[3],
+                          b.x + term[4], b.y + term[5], b.z + term[6], b.w + term[7]};
+      reinterpret_cast<uint4*>(out)[row * chunks + c] =
+          make_uint4(pack_bf16(f[0], f[1]), pack_bf16(f[2], f[3]), pack_bf16(f[4], f[5]), pack_bf16(f[6], f[7]));
+    }
+  }
+}
+
 int block_threads(int chunks) {
   int threads = ((chunks + 31) / 32) * 32;
   return threads > 512 ? 512 : threads;
@@ -178,6 +251,27 @@ cudaError_t launch_merge_bwd(const MergeBwdParams& params, cudaStream_t stream) 
   if (params.blocks == 0) return cudaSuccess;
   merge_bwd_kernel<<<static_cast<unsigned>(params.blocks), block_threads(params.heads * kDim / kChunk), 0, stream>>>(
       params);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_gate_merge(const float* fine, const int64_t* slot_row, const int32_t* block_coarse,
+                              const __nv_bfloat16* gate, const __nv_bfloat16* coarse, __nv_bfloat16* o_slots,
+                              __nv_bfloat16* out, long long blocks, int heads, long long out_rows,
+                              cudaStream_t stream) {
+  if (blocks == 0) return cudaSuccess;
+  const int width = heads * kDim;
+  gate_merge_kernel<<<static_cast<unsigned>(blocks), block_threads(width / kChunk), 0, stream>>>(
+      fine, slot_row, block_coarse, gate, coarse, o_slots, out, width, out_rows);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_grad_finish(const float* acc, const int64_t* slot_row, const void* pool, int pool_f32,
+                               const int32_t* block_map, const int32_t* sizes, __nv_bfloat16* out, long long blocks,
+                               int heads, long long out_rows, cudaStream_t stream) {
+  if (blocks == 0) return cudaSuccess;
+  const int width = heads * kDim;
+  grad_finish_kernel<<<static_cast<unsigned>(blocks), block_threads(width / kChunk), 0, stream>>>(
+      acc, slot_row, pool, pool_f32, block_map, sizes, out, width, out_rows);
   return cudaGetLastError();
 }
 

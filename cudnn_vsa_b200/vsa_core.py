@@ -46,6 +46,8 @@ class _CoarsePlan:
     counts: torch.Tensor        # int32 [q_rows/64]
     kv_sizes: torch.Tensor      # int32 [kv_rows/64]
     q_sizes: torch.Tensor       # int32 [q_rows/64]
+    q_src: torch.Tensor         # int64 [q_rows]: local block whose token sits in each row, -1 = padding
+    kv_src: torch.Tensor        # int64 [kv_rows]: source (global) block of each row, -1 = padding
 
 
 @dataclass
@@ -81,7 +83,14 @@ def _coarse_plan(pairs, q_blocks, kv_blocks, device):
 
     def dev(a):
         return torch.from_numpy(np.ascontiguousarray(a)).to(device)
-    return _CoarsePlan(q_rows=q_chunks * BLOCK, kv_rows=kv_chunks * BLOCK, block_q=dev(block_q),
+
+    def inverse(rows_of_block, rows):
+        src = np.full(rows, -1, dtype=np.int64)
+        used = rows_of_block >= 0
+        src[rows_of_block[used]] = np.nonzero(used)[0]
+        return src
+    return _CoarsePlan(q_src=dev(inverse(block_q, q_chunks * BLOCK)), kv_src=dev(inverse(block_kv, kv_chunks * BLOCK)),
+                       q_rows=q_chunks * BLOCK, kv_rows=kv_chunks * BLOCK, block_q=dev(block_q),
                        block_kv=dev(block_kv), index=dev(index), counts=dev(counts),
                        kv_sizes=dev(np.asarray(kv_sizes or [0], dtype=np.int32)),
                        q_sizes=dev(np.asarray(q_sizes or [0], dtype=np.int32)))

@@ -152,6 +152,22 @@ int vsa_partition_indices(const int32_t* index, const int32_t* counts, const int
 int vsa_merge_partial(float* out, float* lse, const void* part, const float* part_lse, int64_t slots, int32_t heads,
                       void* stream);
 
+/* Ring: last step of the forward pass.  fine: running FP32 output in slot order [blocks*64, width];
+ * writes its BF16 copy to o_slots (null: not wanted) and out[slot_row[slot]] = fine + gate *
+ * coarse[block_coarse[block]] (same rules as the merge epilogue of vsa_fine_fwd).
+ * Replaces the `.to(bf16)` of vsa_core.py:243 plus vsa.py:111-117 on the ring path. */
+int vsa_gate_merge(const float* fine, const int64_t* slot_row, const int32_t* block_coarse, const void* gate,
+                   const void* coarse, void* o_slots, void* out, int64_t blocks, int32_t heads, int64_t out_rows,
+                   void* stream);
+
+/* Ring: last step of the backward pass.  acc: FP32 gradient in slot order; writes
+ * out[slot_row[slot]] = acc[slot] + pool[row] / max(size, 1) as BF16, where pool is FP32 indexed
+ * by block (pool_f32 = 1) or BF16 indexed by block_map[block] (pool_f32 = 0), or null.
+ * Replaces the `.to(q.dtype)` of vsa_core.py:285, the pooling adjoint and the slot->row gather. */
+int vsa_grad_finish(const float* acc, const int64_t* slot_row, const void* pool, int32_t pool_f32,
+                    const int32_t* block_map, const int32_t* block_sizes, void* out, int64_t blocks, int32_t heads,
+                    int64_t out_rows, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

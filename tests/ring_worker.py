@@ -1,0 +1,64 @@
+"""torchrun worker: ring VSA on R GPUs against the single-device result on the same seeded data.
+
+    torchrun --nnodes=1 --nproc-per-node R --master-addr 127.0.0.1 tests/ring_worker.py [geometry ...]
+
+Every rank builds the full block-order layout and its own ring shard, runs both paths on
+identical global inputs and compares output and all four gradients on the rows it owns.
+"""
+import os
+import sys
+from pathlib import Path
+
+import torch
+import torch.distributed as dist
+
+sys.path.insert(0, str(Path(__file__).resolve().parent.parent))
+
+from cudnn_vsa_b200 import vsa_core  # noqa: E402
+from cudnn_vsa_b200.vsa import raster_to_block_wo_padding, vsa_attention  # noqa: E402
+from cudnn_vsa_b200.vsa_layout import build_vsa_layout  # noqa: E402
+from tests.helpers import GEOMETRIES, assert_close, seeded  # noqa: E402
+
+
+def main():
+    names = sys.argv[1:] or ["ragged", "mixed", "fine_only_peer", "partial_blocks", "c1", "dense"]
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    torch.cuda.set_device(int(os.environ["LOCAL_RANK"]))
+    device = torch.device("cuda", int(os.environ["LOCAL_RANK"]))
+    dist.init_process_group("nccl", device_id=device)
+    heads = 2
+    for name in names:
+        for partition in ("cyclic", "contiguous"):
+            samples = GEOMETRIES[name]
+            full = build_vsa_layout(samples, head_num=heads, device=device, input_order="block")
+            if full.blocks < world:
+                continue
+            local = build_vsa_layout(samples, head_num=heads, device=device, input_order="block",
+                                     ring_cp_group=dist.group.WORLD, ring_partition=partition)
+            raster = [x.to(device) for x in seeded(full.tokens, heads, 0, 4)]
+            dy = seeded(full.tokens, heads, 1, 1)[0].to(device)
+            results = []
+            for layout in (full, local):
+                leaves = [raster_to_block_wo_padding(x, vsa_layout=layout).detach().requires_grad_() for x in raster]
+                out = vsa_attention(*leaves, layout)
+                grads = torch.autograd.grad(out, leaves, raster_to_block_wo_padding(dy, vsa_layout=layout),
+                                            allow_unused=True)
+                vsa_core.check_status(layout)
+                results.append((out, *grads))
+            position = torch.empty(full.tokens, dtype=torch.int64, device=device)
+            position[full.input_rows] = torch.arange(full.tokens, device=device)
+            mine = position[local.input_rows]
+            for tag, a, b in zip(("out", "dq", "dk", "dv", "dgate"), results[1], results[0]):
+                if a is None and b is None:
+                    continue
+                b = torch.zeros_like(results[0][0]) if b is None else b
+                a = torch.zeros_like(results[1][0]) if a is None else a
+                assert_close(a, b[mine], f"{name}/{partition}/rank{rank} {tag}", max_abs=2e-2, rel_l2=1e-2)
+            dist.barrier(device_ids=[device.index])
+            if rank == 0:
+                print(f"ring{world} {name} {partition}: ok", flush=True)
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()
