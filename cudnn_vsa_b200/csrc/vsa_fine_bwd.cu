@@ -1,14 +1,17 @@
 // Block-sparse fine attention, backward, for sm_100a: two tcgen05 kernels without atomics.
 //
 //   dQ kernel   one CTA per (query block, head), walks the block's KV list like the forward:
-//               S = Q K^T, dP = dO V^T, dS = P * (dP - delta) * scale, dQ += dS K.
+//               S = Q K^T, dP = dO V^T, dS = P * (dP - delta) * scale, dQ^T += K^T dS^T.
 //   dK/dV kernel one CTA per (KV block, head), walks the query blocks that list this KV block
 //               (a per-call bitmask built by build_kv_mask_kernel):
-//               S^T = K Q^T, dP^T = V dO^T, dV += P^T dO, dK += dS^T Q.
+//               S^T = K Q^T, dP^T = V dO^T, dV^T += dO^T P, dK^T += Q^T dS.
 //
-// P is recomputed from the saved LSE (natural log), so no softmax state is carried.  The
-// epilogues add the gradient that reaches a row through its block's pooled mean and scatter
-// the rows straight to the caller's row order, skipping padding slots.  Together they replace
+// The 64 x 64 score products run with M = 64; the three "x 128-wide" gradient products are kept
+// transposed (head dim on the M axis) so that they run with M = 128, the tensor core's full-rate
+// shape, and each accumulator needs only 64 TMEM columns: two CTAs fit on an SM.  P is
+// recomputed from the saved LSE (natural log), so no softmax state is carried.  The epilogues
+// add the gradient that reaches a row through its block's pooled mean and scatter the rows
+// straight to the caller's row order, skipping padding slots.  Together they replace
 // the reference's fine backward call and its slot-to-row gathers
 // (reference vsa_core.py:23-30, 42-47; vsa_kernels.py:86-96, 161-176 adjoint).
 #include "vsa_common.cuh"
@@ -38,101 +41,69 @@ VSA_DEVICE void issue_nt_128(uint32_t tmem_d, const uint8_t* a, const uint8_t* b
   }
 }
 
-// D[64 x 128] (+)= A[64 x 64] B[64 x 128]: A K-major (one 64-wide tile), B a row-major tile
-// read as MN-major (its rows are the K index).
-VSA_DEVICE void issue_nn_64(uint32_t tmem_d, const uint8_t* a, const uint8_t* b, bool accumulate) {
-  constexpr uint32_t idesc = umma_idesc(64, 128, 0, 1);
+// D^T[128 x 64] (+)= A^T B with A a row-major [64 rows][128 dims] tile read MN-major (M = dims,
+// K = its rows) and B a K-major [64 rows][64] tile whose rows are the N index: the M = 128 form of
+// the "x 128-wide output" products (dQ^T = K^T dS^T, dV^T = dO^T P, dK^T = Q^T dS).
+VSA_DEVICE void issue_tn_128(uint32_t tmem_d, const uint8_t* a, const uint8_t* b, bool accumulate) {
+  constexpr uint32_t idesc = umma_idesc(128, 64, 1, 0);
 #pragma unroll
   for (int ks = 0; ks < 4; ++ks) {
-    umma_ss(tmem_d, umma_smem_desc(smem_u32(a) + ks * 32, 16, 1024),
-            umma_smem_desc(smem_u32(b) + ks * 2048, kHalfTileBytes, 1024), idesc, accumulate || ks > 0);
+    umma_ss(tmem_d, umma_smem_desc(smem_u32(a) + ks * 2048, kHalfTileBytes, 1024),
+            umma_smem_desc(smem_u32(b) + ks * 32, 16, 1024), idesc, accumulate || ks > 0);
   }
 }
 
-VSA_DEVICE void bulk_load(void* smem_dst, const void* gmem_src, uint32_t bytes, uint64_t* bar) {
-  asm volatile(
-      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-      ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(gmem_src)), "r"(bytes), "r"(smem_u32(bar))
-      : "memory");
-}
-
-// Pooled-mean gradient of `block` for this thread's 64 columns, already divided by the block size.
-VSA_DEVICE void load_pool_term(float (&term)[64], const void* pool, int pool_f32, const int32_t* block_coarse,
-                               int block, int size, long long width, long long col) {
+// Pooled-mean gradient of `block` at column `col`, already divided by the block size.
+VSA_DEVICE float pool_term(const void* pool, int pool_f32, const int32_t* block_coarse, int block, int size,
+                           long long width, long long col) {
   long long prow = -1;
   if (pool != nullptr) prow = pool_f32 ? block : (block_coarse != nullptr ? block_coarse[block] : -1);
-  if (prow < 0) {
-#pragma unroll
-    for (int i = 0; i < 64; ++i) term[i] = 0.f;
-    return;
-  }
+  if (prow < 0) return 0.f;
   const float inv = 1.f / static_cast<float>(size > 1 ? size : 1);
-  if (pool_f32) {
-    const float4* src = reinterpret_cast<const float4*>(static_cast<const float*>(pool) + prow * width + col);
-#pragma unroll
-    for (int c = 0; c < 16; ++c) {
-      const float4 f = __ldg(src + c);
-      term[4 * c] = f.x * inv, term[4 * c + 1] = f.y * inv, term[4 * c + 2] = f.z * inv, term[4 * c + 3] = f.w * inv;
-    }
-  } else {
-    const uint4* src = reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(pool) + prow * width + col);
-#pragma unroll
-    for (int c = 0; c < 8; ++c) {
-      const uint4 u = __ldg(src + c);
-      const uint32_t w[4] = {u.x, u.y, u.z, u.w};
-#pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const float2 f = unpack_bf16(w[e]);
-        term[8 * c + 2 * e] = f.x * inv, term[8 * c + 2 * e + 1] = f.y * inv;
-      }
-    }
-  }
+  const float value = pool_f32 ? static_cast<const float*>(pool)[prow * width + col]
+                               : __bfloat162float(static_cast<const __nv_bfloat16*>(pool)[prow * width + col]);
+  return value * inv;
 }
 
-// Reads this thread's 64 accumulator columns (or zeros), adds the pooled term and stores the row:
-// BF16 to `dst_row` when `write`, or FP32 into `f32_row` (added to its content when `accumulate`).
-VSA_DEVICE void store_grad_row(__nv_bfloat16* dst_row, bool have_acc, uint32_t tmem_addr, const float (&term)[64],
-                               bool write, float* f32_row, bool accumulate) {
-  float acc[64];
+// Epilogue of a transposed accumulator: this thread owns head dim `col % 128`, its 64 columns are
+// the 64 slots of `block`.  Adds `term` and writes BF16 to the mapped rows of `out`, or FP32 in
+// slot order (added to the buffer's content when `accumulate`).  A warp store covers 32
+// consecutive elements of one row.
+VSA_DEVICE void store_grad_columns(bool have_acc, uint32_t tmem_addr, float term, const long long* out_rows,
+                                   long long out_limit, __nv_bfloat16* out, float* out_f32, bool accumulate,
+                                   long long block, long long width, long long col) {
 #pragma unroll
   for (int c = 0; c < 2; ++c) {
     uint32_t bits[32] = {};
     if (have_acc) {
-      VSA_TMEM_LD_16x32bx2_X32(bits, tmem_addr + c * 32, 64);
+      VSA_TMEM_LD_32x32b_X32(bits, tmem_addr + c * 32);
       tmem_wait_ld();
     }
 #pragma unroll
-    for (int i = 0; i < 32; ++i) acc[c * 32 + i] = __uint_as_float(bits[i]) + term[c * 32 + i];
-  }
-  if (f32_row != nullptr) {
-    float4* dst = reinterpret_cast<float4*>(f32_row);
-#pragma unroll
-    for (int c = 0; c < 16; ++c) {
-      float4 v = make_float4(acc[4 * c], acc[4 * c + 1], acc[4 * c + 2], acc[4 * c + 3]);
-      if (accumulate) {
-        const float4 old = dst[c];
-        v.x += old.x, v.y += old.y, v.z += old.z, v.w += old.w;
+    for (int i = 0; i < 32; ++i) {
+      const int r = c * 32 + i;
+      const float value = __uint_as_float(bits[i]) + term;
+      if (out_f32 != nullptr) {
+        float* dst = out_f32 + (block * kBlock + r) * width + col;
+        *dst = accumulate ? *dst + value : value;
+      } else {
+        const long long row = out_rows[r];
+        if (row >= 0 && row < out_limit) out[row * width + col] = __float2bfloat16(value);
       }
-      dst[c] = v;
     }
-  } else if (write) {
-    uint4* dst = reinterpret_cast<uint4*>(dst_row);
-#pragma unroll
-    for (int c = 0; c < 8; ++c)
-      dst[c] = make_uint4(pack_bf16(acc[8 * c], acc[8 * c + 1]), pack_bf16(acc[8 * c + 2], acc[8 * c + 3]),
-                          pack_bf16(acc[8 * c + 4], acc[8 * c + 5]), pack_bf16(acc[8 * c + 6], acc[8 * c + 7]));
   }
 }
 
 // ------------------------------------------------------------------------------------------ dQ
-constexpr int kDqTmemCols = 256;  // S [0,64)  dP [64,128)  dQ [128,256)
+constexpr int kDqTmemCols = 256;  // S [0,64)  dP [64,128)  dQ^T [128,192)
 
-struct __align__(1024) DqSmem {
+struct DqSmem {  // placed at a 1024-byte aligned address
   uint8_t q[kTileBytes];
   uint8_t d_o[kTileBytes];
   uint8_t k[2][kTileBytes];
   uint8_t v[2][kTileBytes];
   uint8_t ds[kHalfTileBytes];
+  long long out_row[kBlock];
   uint64_t qdo_full, kv_full[2], sp_done, dq_done;
   uint32_t tmem_base;
   int abort_flag;
@@ -140,7 +111,7 @@ struct __align__(1024) DqSmem {
 
 }  // namespace
 
-__global__ void __launch_bounds__(kThreads) fine_bwd_dq_kernel(const __grid_constant__ FineBwdParams p) {
+__global__ void __launch_bounds__(kThreads, 2) fine_bwd_dq_kernel(const __grid_constant__ FineBwdParams p) {
   extern __shared__ uint8_t smem_raw[];
   DqSmem& sm = *reinterpret_cast<DqSmem*>(smem_raw + ((1024 - (smem_u32(smem_raw) & 1023)) & 1023));
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -159,6 +130,10 @@ __global__ void __launch_bounds__(kThreads) fine_bwd_dq_kernel(const __grid_cons
     mbar_init(&sm.dq_done, 1);
     sm.abort_flag = 0;
     fence_barrier_init();
+  }
+  if (tid < kBlock) {
+    const long long s = static_cast<long long>(qb) * kBlock + tid;
+    sm.out_row[tid] = p.q_slot_row != nullptr ? p.q_slot_row[s] : s;
   }
   if (warp == 0) {
     tmem_alloc(&sm.tmem_base, kDqTmemCols);
@@ -212,7 +187,7 @@ __global__ void __launch_bounds__(kThreads) fine_bwd_dq_kernel(const __grid_cons
 #pragma unroll
       for (int e = 0; e < 2; ++e) {
         const bool live = row_live && (half * 32 + i + e < kv_size);
-        const float pr = live ? fast_exp2(__uint_as_float(s_bits[i + e]) * sl2 - lse2) : 0.f;
+        const float pr = live ? fast_exp2(fmaf(__uint_as_float(s_bits[i + e]), sl2, -lse2)) : 0.f;
         ds[e] = pr * (__uint_as_float(dp_bits[i + e]) - delta) * p.scale;
       }
       packed[i >> 1] = pack_bf16(ds[0], ds[1]);
@@ -237,7 +212,7 @@ __global__ void __launch_bounds__(kThreads) fine_bwd_dq_kernel(const __grid_cons
     __syncthreads();
     if (tid == 0) {
       tc_fence_after();
-      issue_nn_64(tmem + 128, sm.ds, sm.k[b], j > 0);
+      issue_tn_128(tmem + 128, sm.k[b], sm.ds, j > 0);  // dQ^T += K^T dS^T
       umma_commit(&sm.dq_done);
       if (j + 1 < n) {
         mbar_wait(&sm.kv_full[b ^ 1], ((j + 1) >> 1) & 1, abort_flag, p.status, 15);
@@ -255,14 +230,11 @@ __global__ void __launch_bounds__(kThreads) fine_bwd_dq_kernel(const __grid_cons
     tc_fence_after();
   }
   const long long width = static_cast<long long>(p.heads) * kDim;
-  const long long col = static_cast<long long>(head) * kDim + half * 64;
-  const long long out_row = p.q_slot_row != nullptr ? p.q_slot_row[slot] : slot;
+  const long long col = static_cast<long long>(head) * kDim + tid;
   const int q_size = p.q_sizes != nullptr ? p.q_sizes[qb] : kBlock;
-  float term[64];
-  load_pool_term(term, p.dq_pool, p.pool_f32, p.q_block_coarse, qb, q_size, width, col);
-  const bool write = out_row >= 0 && out_row < p.q_out_rows;
-  store_grad_row(p.dq + (write ? out_row : 0) * width + col, n > 0, tmem + lane_base + 128, term, write,
-                 p.dq_f32 != nullptr ? p.dq_f32 + slot * width + col : nullptr, p.f32_accumulate != 0);
+  const float term = pool_term(p.dq_pool, p.pool_f32, p.q_block_coarse, qb, q_size, width, col);
+  store_grad_columns(n > 0, tmem + lane_base + 128, term, sm.out_row, p.q_out_rows, p.dq, p.dq_f32,
+                     p.f32_accumulate != 0, qb, width, col);
   tc_fence_before();
   __syncthreads();
   if (warp == 0) tmem_dealloc(tmem, kDqTmemCols);
@@ -271,18 +243,20 @@ __global__ void __launch_bounds__(kThreads) fine_bwd_dq_kernel(const __grid_cons
 // ------------------------------------------------------------------------------------------ dK, dV
 namespace {
 
-constexpr int kDkvTmemCols = 512;  // S^T [0,64)  dP^T [64,128)  dK [128,256)  dV [256,384)
+constexpr int kDkvTmemCols = 256;  // S^T [0,64)  dP^T [64,128)  dK^T [128,192)  dV^T [192,256)
 
-struct __align__(1024) DkvSmem {
+// Exactly 112 KiB of tiles plus the barriers: two CTAs fit on an SM only without an alignment
+// pad, so the kernel requires (and checks) a 1024-byte aligned dynamic shared memory base.
+struct DkvSmem {
   uint8_t k[kTileBytes];
   uint8_t v[kTileBytes];
   uint8_t q[2][kTileBytes];
   uint8_t d_o[2][kTileBytes];
   uint8_t pt[kHalfTileBytes];
   uint8_t dst[kHalfTileBytes];
-  float lse[2][kBlock];
-  float delta[2][kBlock];
+  long long out_row[kBlock];
   uint64_t kv_full, qd_full[2], sp_done, dkv_done;
+  int stage_block[2];
   uint32_t tmem_base;
   int abort_flag;
 };
@@ -304,13 +278,18 @@ struct MaskCursor {
 
 }  // namespace
 
-__global__ void __launch_bounds__(kThreads) fine_bwd_dkv_kernel(const __grid_constant__ FineBwdParams p) {
-  extern __shared__ uint8_t smem_raw[];
-  DkvSmem& sm = *reinterpret_cast<DkvSmem*>(smem_raw + ((1024 - (smem_u32(smem_raw) & 1023)) & 1023));
+__global__ void __launch_bounds__(kThreads, 2) fine_bwd_dkv_kernel(const __grid_constant__ FineBwdParams p) {
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  DkvSmem& sm = *reinterpret_cast<DkvSmem*>(smem_raw);
+  if ((smem_u32(smem_raw) & 1023) != 0) {
+    // The swizzled tiles need 1024-byte alignment; report instead of computing garbage.
+    if (threadIdx.x == 0 && p.status != nullptr) atomicCAS(p.status, 0, kDevWaitTimeout + 99);
+    return;
+  }
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int kvb = blockIdx.x, head = blockIdx.y;
-  const int row = warp * 16 + (lane & 15);  // KV slot inside the block
-  const int half = lane >> 4;               // which 32 query columns / 64 output columns
+  const int row = warp * 16 + (lane & 15);  // KV slot inside the block (softmax role)
+  const int half = lane >> 4;               // which 32 query columns
   const uint32_t* mask = p.kv_mask + (static_cast<long long>(head) * p.kv_blocks + kvb) * p.mask_words;
   int n = 0;
   for (int w = 0; w < p.mask_words; ++w) n += __popc(mask[w]);
@@ -324,9 +303,26 @@ __global__ void __launch_bounds__(kThreads) fine_bwd_dkv_kernel(const __grid_con
     sm.abort_flag = 0;
     fence_barrier_init();
   }
+  if (tid < kBlock) {
+    const long long s = static_cast<long long>(kvb) * kBlock + tid;
+    sm.out_row[tid] = p.kv_slot_row != nullptr ? p.kv_slot_row[s] : s;
+  }
   if (warp == 0) {
     tmem_alloc(&sm.tmem_base, kDkvTmemCols);
     tmem_relinquish();
+  }
+  MaskCursor cursor{mask, p.mask_words, 0, (tid == 0 && p.mask_words > 0) ? mask[0] : 0u};
+  auto load_stage = [&](int stage, int q_block) {
+    sm.stage_block[stage] = q_block;
+    mbar_expect_tx(&sm.qd_full[stage], 2 * kTileBytes);
+    tma_load_tile(sm.q[stage], &p.q_map, &sm.qd_full[stage], head, q_block);
+    tma_load_tile(sm.d_o[stage], &p.do_map, &sm.qd_full[stage], head, q_block);
+  };
+  if (tid == 0 && n > 0) {
+    mbar_expect_tx(&sm.kv_full, 2 * kTileBytes);
+    tma_load_tile(sm.k, &p.k_map, &sm.kv_full, head, kvb);
+    tma_load_tile(sm.v, &p.v_map, &sm.kv_full, head, kvb);
+    for (int s = 0; s < 2 && s < n; ++s) load_stage(s, cursor.next());
   }
   tc_fence_before();
   __syncthreads();
@@ -334,21 +330,7 @@ __global__ void __launch_bounds__(kThreads) fine_bwd_dkv_kernel(const __grid_con
   const uint32_t tmem = sm.tmem_base;
   const uint32_t lane_base = static_cast<uint32_t>(warp * 32) << 16;
   volatile int* abort_flag = &sm.abort_flag;
-
-  MaskCursor cursor{mask, p.mask_words, 0, (tid == 0 && p.mask_words > 0) ? mask[0] : 0u};
-  auto load_stage = [&](int stage, int q_block) {
-    mbar_expect_tx(&sm.qd_full[stage], 2 * kTileBytes + 2 * kBlock * 4);
-    tma_load_tile(sm.q[stage], &p.q_map, &sm.qd_full[stage], head, q_block);
-    tma_load_tile(sm.d_o[stage], &p.do_map, &sm.qd_full[stage], head, q_block);
-    const long long off = static_cast<long long>(head) * p.q_slots + static_cast<long long>(q_block) * kBlock;
-    bulk_load(sm.lse[stage], p.lse + off, kBlock * 4, &sm.qd_full[stage]);
-    bulk_load(sm.delta[stage], p.delta + off, kBlock * 4, &sm.qd_full[stage]);
-  };
   if (tid == 0 && n > 0) {
-    mbar_expect_tx(&sm.kv_full, 2 * kTileBytes);
-    tma_load_tile(sm.k, &p.k_map, &sm.kv_full, head, kvb);
-    tma_load_tile(sm.v, &p.v_map, &sm.kv_full, head, kvb);
-    for (int s = 0; s < 2 && s < n; ++s) load_stage(s, cursor.next());
     mbar_wait(&sm.kv_full, 0, abort_flag, p.status, 21);
     mbar_wait(&sm.qd_full[0], 0, abort_flag, p.status, 22);
     tc_fence_after();
@@ -363,10 +345,20 @@ __global__ void __launch_bounds__(kThreads) fine_bwd_dkv_kernel(const __grid_con
 
   for (int j = 0; j < n; ++j) {
     const int b = j & 1;
+    // LSE and delta of this thread's 32 query columns, straight from global memory (L2-resident,
+    // identical addresses across the threads of a half), issued before the MMA wait.
+    const long long stat = static_cast<long long>(head) * p.q_slots +
+                           static_cast<long long>(sm.stage_block[b]) * kBlock + half * 32;
+    float lse2[32], delta[32];
+#pragma unroll
+    for (int c = 0; c < 8; ++c) {
+      const float4 a = __ldg(reinterpret_cast<const float4*>(p.lse + stat) + c);
+      const float4 d = __ldg(reinterpret_cast<const float4*>(p.delta + stat) + c);
+      lse2[4 * c] = a.x * kLog2e, lse2[4 * c + 1] = a.y * kLog2e, lse2[4 * c + 2] = a.z * kLog2e,
+      lse2[4 * c + 3] = a.w * kLog2e;
+      delta[4 * c] = d.x, delta[4 * c + 1] = d.y, delta[4 * c + 2] = d.z, delta[4 * c + 3] = d.w;
+    }
     mbar_wait(&sm.sp_done, j & 1, abort_flag, p.status, 23);
-    // Every thread observes the stage's own barrier before reading the LSE / delta rows that
-    // the bulk copies wrote.
-    mbar_wait(&sm.qd_full[b], (j >> 1) & 1, abort_flag, p.status, 24);
     tc_fence_after();
     uint32_t s_bits[32], dp_bits[32];
     VSA_TMEM_LD_16x32bx2_X32(s_bits, tmem + lane_base, 32);
@@ -378,11 +370,9 @@ __global__ void __launch_bounds__(kThreads) fine_bwd_dkv_kernel(const __grid_con
       float pr[2], ds[2];
 #pragma unroll
       for (int e = 0; e < 2; ++e) {
-        const int c = half * 32 + i + e;
-        const float lse = sm.lse[b][c];
-        const bool live = key_live && lse != -INFINITY;
-        pr[e] = live ? fast_exp2(__uint_as_float(s_bits[i + e]) * sl2 - lse * kLog2e) : 0.f;
-        ds[e] = pr[e] * (__uint_as_float(dp_bits[i + e]) - sm.delta[b][c]) * p.scale;
+        const bool live = key_live && lse2[i + e] != -INFINITY;
+        pr[e] = live ? fast_exp2(fmaf(__uint_as_float(s_bits[i + e]), sl2, -lse2[i + e])) : 0.f;
+        ds[e] = pr[e] * (__uint_as_float(dp_bits[i + e]) - delta[i + e]) * p.scale;
       }
       p_packed[i >> 1] = pack_bf16(pr[0], pr[1]);
       ds_packed[i >> 1] = pack_bf16(ds[0], ds[1]);
@@ -407,8 +397,8 @@ __global__ void __launch_bounds__(kThreads) fine_bwd_dkv_kernel(const __grid_con
     __syncthreads();
     if (tid == 0) {
       tc_fence_after();
-      issue_nn_64(tmem + 256, sm.pt, sm.d_o[b], j > 0);  // dV += P^T dO
-      issue_nn_64(tmem + 128, sm.dst, sm.q[b], j > 0);   // dK += dS^T Q
+      issue_tn_128(tmem + 192, sm.d_o[b], sm.pt, j > 0);  // dV^T += dO^T P
+      issue_tn_128(tmem + 128, sm.q[b], sm.dst, j > 0);   // dK^T += Q^T dS
       umma_commit(&sm.dkv_done);
       if (j + 1 < n) {
         mbar_wait(&sm.qd_full[b ^ 1], ((j + 1) >> 1) & 1, abort_flag, p.status, 26);
@@ -425,18 +415,14 @@ __global__ void __launch_bounds__(kThreads) fine_bwd_dkv_kernel(const __grid_con
     mbar_wait(&sm.dkv_done, (n - 1) & 1, abort_flag, p.status, 27);
     tc_fence_after();
   }
-  const long long slot = static_cast<long long>(kvb) * kBlock + row;
   const long long width = static_cast<long long>(p.heads) * kDim;
-  const long long col = static_cast<long long>(head) * kDim + half * 64;
-  const long long out_row = p.kv_slot_row != nullptr ? p.kv_slot_row[slot] : slot;
-  const bool write = out_row >= 0 && out_row < p.kv_out_rows;
-  float term[64];
-  load_pool_term(term, p.dk_pool, p.pool_f32, p.kv_block_coarse, kvb, kv_size, width, col);
-  store_grad_row(p.dk + (write ? out_row : 0) * width + col, n > 0, tmem + lane_base + 128, term, write,
-                 p.dk_f32 != nullptr ? p.dk_f32 + slot * width + col : nullptr, p.f32_accumulate != 0);
-  load_pool_term(term, p.dv_pool, p.pool_f32, p.kv_block_coarse, kvb, kv_size, width, col);
-  store_grad_row(p.dv + (write ? out_row : 0) * width + col, n > 0, tmem + lane_base + 256, term, write,
-                 p.dv_f32 != nullptr ? p.dv_f32 + slot * width + col : nullptr, p.f32_accumulate != 0);
+  const long long col = static_cast<long long>(head) * kDim + tid;
+  float term = pool_term(p.dk_pool, p.pool_f32, p.kv_block_coarse, kvb, kv_size, width, col);
+  store_grad_columns(n > 0, tmem + lane_base + 128, term, sm.out_row, p.kv_out_rows, p.dk, p.dk_f32,
+                     p.f32_accumulate != 0, kvb, width, col);
+  term = pool_term(p.dv_pool, p.pool_f32, p.kv_block_coarse, kvb, kv_size, width, col);
+  store_grad_columns(n > 0, tmem + lane_base + 192, term, sm.out_row, p.kv_out_rows, p.dv, p.dv_f32,
+                     p.f32_accumulate != 0, kvb, width, col);
   tc_fence_before();
   __syncthreads();
   if (warp == 0) tmem_dealloc(tmem, kDkvTmemCols);
@@ -481,9 +467,7 @@ cudaError_t launch_fine_bwd_dq(const FineBwdParams& params, cudaStream_t stream)
 }
 
 cudaError_t launch_fine_bwd_dkv(const FineBwdParams& params, cudaStream_t stream) {
-  // 512 TMEM columns per CTA: ask for more than half of the SM's shared memory so that two CTAs
-  // can never be resident together and wait on each other's tensor memory.
-  const size_t smem = sizeof(DkvSmem) + 1024 > 120 * 1024 ? sizeof(DkvSmem) + 1024 : 120 * 1024;
+  const size_t smem = sizeof(DkvSmem);
   cudaError_t err = cudaFuncSetAttribute(fine_bwd_dkv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          static_cast<int>(smem));
   if (err != cudaSuccess) return err;
