@@ -75,6 +75,28 @@ VSA_DEVICE bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_fl
   return true;
 }
 
+// One arrival (release) on an mbarrier whose expected count is the number of arriving threads.
+VSA_DEVICE void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+// Named barrier `id` over `threads` threads (a subset of the CTA's warps), and the same with an
+// OR reduction of a per-thread predicate.
+VSA_DEVICE void named_barrier(int id, int threads) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
+}
+VSA_DEVICE bool named_barrier_or(int id, int threads, bool value) {
+  uint32_t out;
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\t"
+      "setp.ne.b32 q, %3, 0;\n\t"
+      "bar.red.or.pred p, %1, %2, q;\n\t"
+      "selp.b32 %0, 1, 0, p;\n\t}"
+      : "=r"(out)
+      : "r"(id), "r"(threads), "r"(static_cast<uint32_t>(value))
+      : "memory");
+  return out != 0;
+}
+
 VSA_DEVICE void fence_barrier_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
 // Make generic-proxy shared-memory writes visible to the async proxy (TMA, tcgen05.mma).
 VSA_DEVICE void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }

@@ -21,7 +21,8 @@ namespace vsa {
 
 namespace {
 
-constexpr int kThreads = 128;
+constexpr int kSoftmaxThreads = 128;  // warps 0..3: score math and epilogue
+constexpr int kThreads = 160;         // warp 4: TMA and tcgen05.mma issue
 constexpr float kLog2e = 1.4426950408889634f;
 
 VSA_DEVICE float fast_exp2(float x) {
@@ -104,7 +105,7 @@ struct DqSmem {  // placed at a 1024-byte aligned address
   uint8_t v[2][kTileBytes];
   uint8_t ds[kHalfTileBytes];
   long long out_row[kBlock];
-  uint64_t qdo_full, kv_full[2], sp_done, dq_done;
+  uint64_t qdo_full, kv_full[2], sp_done, dq_done, sp_free, ds_ready;
   uint32_t tmem_base;
   int abort_flag;
 };
@@ -116,7 +117,7 @@ __global__ void __launch_bounds__(kThreads, 2) fine_bwd_dq_kernel(const __grid_c
   DqSmem& sm = *reinterpret_cast<DqSmem*>(smem_raw + ((1024 - (smem_u32(smem_raw) & 1023)) & 1023));
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int qb = blockIdx.x, head = blockIdx.y;
-  const int row = warp * 16 + (lane & 15);
+  const int row = (warp & 3) * 16 + (lane & 15);
   const int half = lane >> 4;
   const int n = p.counts[static_cast<long long>(head) * p.count_head_stride + qb];
   const int32_t* list = p.indices + static_cast<long long>(head) * p.index_head_stride +
@@ -128,6 +129,8 @@ __global__ void __launch_bounds__(kThreads, 2) fine_bwd_dq_kernel(const __grid_c
     mbar_init(&sm.kv_full[1], 1);
     mbar_init(&sm.sp_done, 1);
     mbar_init(&sm.dq_done, 1);
+    mbar_init(&sm.sp_free, kSoftmaxThreads);
+    mbar_init(&sm.ds_ready, kSoftmaxThreads);
     sm.abort_flag = 0;
     fence_barrier_init();
   }
@@ -143,98 +146,104 @@ __global__ void __launch_bounds__(kThreads, 2) fine_bwd_dq_kernel(const __grid_c
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = sm.tmem_base;
-  const uint32_t lane_base = static_cast<uint32_t>(warp * 32) << 16;
+  const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
   volatile int* abort_flag = &sm.abort_flag;
 
-  if (tid == 0 && n > 0) {
-    mbar_expect_tx(&sm.qdo_full, 2 * kTileBytes);
-    tma_load_tile(sm.q, &p.q_map, &sm.qdo_full, head, qb);
-    tma_load_tile(sm.d_o, &p.do_map, &sm.qdo_full, head, qb);
-    for (int s = 0; s < 2 && s < n; ++s) {
-      mbar_expect_tx(&sm.kv_full[s], 2 * kTileBytes);
-      tma_load_tile(sm.k[s], &p.k_map, &sm.kv_full[s], head, list[s]);
-      tma_load_tile(sm.v[s], &p.v_map, &sm.kv_full[s], head, list[s]);
-    }
-    mbar_wait(&sm.qdo_full, 0, abort_flag, p.status, 11);
-    mbar_wait(&sm.kv_full[0], 0, abort_flag, p.status, 12);
-    tc_fence_after();
-    issue_nt_128(tmem, sm.q, sm.k[0]);
-    issue_nt_128(tmem + 64, sm.d_o, sm.v[0]);
-    umma_commit(&sm.sp_done);
-  }
-
-  const long long slot = static_cast<long long>(qb) * kBlock + row;
-  const float lse = p.lse[static_cast<long long>(head) * p.q_slots + slot];
-  const float delta = p.delta[static_cast<long long>(head) * p.q_slots + slot];
-  const float sl2 = p.scale * kLog2e;
-  const float lse2 = lse * kLog2e;
-  const bool row_live = lse != -INFINITY;
-
-  for (int j = 0; j < n; ++j) {
-    const int b = j & 1;
-    const int kv_block = list[j];
-    const int kv_size = p.kv_sizes != nullptr ? p.kv_sizes[kv_block] : kBlock;
-    mbar_wait(&sm.sp_done, j & 1, abort_flag, p.status, 13);
-    tc_fence_after();
-    uint32_t s_bits[32], dp_bits[32];
-    VSA_TMEM_LD_16x32bx2_X32(s_bits, tmem + lane_base, 32);
-    VSA_TMEM_LD_16x32bx2_X32(dp_bits, tmem + lane_base + 64, 32);
-    tmem_wait_ld();
-    uint32_t packed[16];
-#pragma unroll
-    for (int i = 0; i < 32; i += 2) {
-      float ds[2];
-#pragma unroll
-      for (int e = 0; e < 2; ++e) {
-        const bool live = row_live && (half * 32 + i + e < kv_size);
-        const float pr = live ? fast_exp2(fmaf(__uint_as_float(s_bits[i + e]), sl2, -lse2)) : 0.f;
-        ds[e] = pr * (__uint_as_float(dp_bits[i + e]) - delta) * p.scale;
+  if (warp == 4) {
+    // ------------------------------------------------------------ issuer: TMA loads and MMAs
+    if (lane == 0 && n > 0) {
+      mbar_expect_tx(&sm.qdo_full, 2 * kTileBytes);
+      tma_load_tile(sm.q, &p.q_map, &sm.qdo_full, head, qb);
+      tma_load_tile(sm.d_o, &p.do_map, &sm.qdo_full, head, qb);
+      for (int s = 0; s < 2 && s < n; ++s) {
+        mbar_expect_tx(&sm.kv_full[s], 2 * kTileBytes);
+        tma_load_tile(sm.k[s], &p.k_map, &sm.kv_full[s], head, list[s]);
+        tma_load_tile(sm.v[s], &p.v_map, &sm.kv_full[s], head, list[s]);
       }
-      packed[i >> 1] = pack_bf16(ds[0], ds[1]);
-    }
-    if (j > 0) {
-      // dQ_{j-1} done: the dS buffer and K/V stage b^1 are free again.
-      mbar_wait(&sm.dq_done, (j - 1) & 1, abort_flag, p.status, 14);
+      mbar_wait(&sm.qdo_full, 0, abort_flag, p.status, 11);
+      mbar_wait(&sm.kv_full[0], 0, abort_flag, p.status, 12);
       tc_fence_after();
-      if (tid == 0 && j + 1 < n) {
-        mbar_expect_tx(&sm.kv_full[b ^ 1], 2 * kTileBytes);
-        tma_load_tile(sm.k[b ^ 1], &p.k_map, &sm.kv_full[b ^ 1], head, list[j + 1]);
-        tma_load_tile(sm.v[b ^ 1], &p.v_map, &sm.kv_full[b ^ 1], head, list[j + 1]);
-      }
-      __syncwarp();
-    }
-#pragma unroll
-    for (int c = 0; c < 4; ++c)
-      *reinterpret_cast<uint4*>(sm.ds + swizzled_offset(row, half * 4 + c)) =
-          make_uint4(packed[4 * c], packed[4 * c + 1], packed[4 * c + 2], packed[4 * c + 3]);
-    fence_proxy_async_smem();
-    tc_fence_before();
-    __syncthreads();
-    if (tid == 0) {
-      tc_fence_after();
-      issue_tn_128(tmem + 128, sm.k[b], sm.ds, j > 0);  // dQ^T += K^T dS^T
-      umma_commit(&sm.dq_done);
-      if (j + 1 < n) {
-        mbar_wait(&sm.kv_full[b ^ 1], ((j + 1) >> 1) & 1, abort_flag, p.status, 15);
+      issue_nt_128(tmem, sm.q, sm.k[0]);
+      issue_nt_128(tmem + 64, sm.d_o, sm.v[0]);
+      umma_commit(&sm.sp_done);
+      for (int j = 0; j < n; ++j) {
+        const int b = j & 1;
+        if (j + 1 < n) {
+          // S_j and dP_j are in registers: the next pair may overwrite them and runs under the
+          // score math of tile j.
+          mbar_wait(&sm.sp_free, j & 1, abort_flag, p.status, 17);
+          mbar_wait(&sm.kv_full[b ^ 1], ((j + 1) >> 1) & 1, abort_flag, p.status, 15);
+          tc_fence_after();
+          issue_nt_128(tmem, sm.q, sm.k[b ^ 1]);
+          issue_nt_128(tmem + 64, sm.d_o, sm.v[b ^ 1]);
+          umma_commit(&sm.sp_done);
+        }
+        mbar_wait(&sm.ds_ready, j & 1, abort_flag, p.status, 18);
         tc_fence_after();
-        issue_nt_128(tmem, sm.q, sm.k[b ^ 1]);
-        issue_nt_128(tmem + 64, sm.d_o, sm.v[b ^ 1]);
-        umma_commit(&sm.sp_done);
+        issue_tn_128(tmem + 128, sm.k[b], sm.ds, j > 0);  // dQ^T += K^T dS^T
+        umma_commit(&sm.dq_done);
+        if (j + 2 < n) {
+          // Stage b is free once dQ_j (the newest commit on this barrier) has read K_j.
+          mbar_wait(&sm.dq_done, j & 1, abort_flag, p.status, 14);
+          mbar_expect_tx(&sm.kv_full[b], 2 * kTileBytes);
+          tma_load_tile(sm.k[b], &p.k_map, &sm.kv_full[b], head, list[j + 2]);
+          tma_load_tile(sm.v[b], &p.v_map, &sm.kv_full[b], head, list[j + 2]);
+        }
       }
     }
-    __syncwarp();
+  } else {
+    // ------------------------------------------------------------ score math warps
+    const long long slot = static_cast<long long>(qb) * kBlock + row;
+    const float lse = p.lse[static_cast<long long>(head) * p.q_slots + slot];
+    const float delta = p.delta[static_cast<long long>(head) * p.q_slots + slot];
+    const float sl2 = p.scale * kLog2e;
+    const float lse2 = lse * kLog2e;
+    const bool row_live = lse != -INFINITY;
+    for (int j = 0; j < n; ++j) {
+      const int kv_block = list[j];
+      const int kv_size = p.kv_sizes != nullptr ? p.kv_sizes[kv_block] : kBlock;
+      mbar_wait(&sm.sp_done, j & 1, abort_flag, p.status, 13);
+      tc_fence_after();
+      uint32_t s_bits[32], dp_bits[32];
+      VSA_TMEM_LD_16x32bx2_X32(s_bits, tmem + lane_base, 32);
+      VSA_TMEM_LD_16x32bx2_X32(dp_bits, tmem + lane_base + 64, 32);
+      tmem_wait_ld();
+      tc_fence_before();
+      mbar_arrive(&sm.sp_free);
+      uint32_t packed[16];
+#pragma unroll
+      for (int i = 0; i < 32; i += 2) {
+        float ds[2];
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          const bool live = row_live && (half * 32 + i + e < kv_size);
+          const float pr = live ? fast_exp2(fmaf(__uint_as_float(s_bits[i + e]), sl2, -lse2)) : 0.f;
+          ds[e] = pr * (__uint_as_float(dp_bits[i + e]) - delta) * p.scale;
+        }
+        packed[i >> 1] = pack_bf16(ds[0], ds[1]);
+      }
+      if (j > 0) {
+        // dQ_{j-1} has finished reading the dS buffer.
+        mbar_wait(&sm.dq_done, (j - 1) & 1, abort_flag, p.status, 14);
+      }
+#pragma unroll
+      for (int c = 0; c < 4; ++c)
+        *reinterpret_cast<uint4*>(sm.ds + swizzled_offset(row, half * 4 + c)) =
+            make_uint4(packed[4 * c], packed[4 * c + 1], packed[4 * c + 2], packed[4 * c + 3]);
+      fence_proxy_async_smem();
+      mbar_arrive(&sm.ds_ready);
+    }
+    if (n > 0) {
+      mbar_wait(&sm.dq_done, (n - 1) & 1, abort_flag, p.status, 16);
+      tc_fence_after();
+    }
+    const long long width = static_cast<long long>(p.heads) * kDim;
+    const long long col = static_cast<long long>(head) * kDim + tid;
+    const int q_size = p.q_sizes != nullptr ? p.q_sizes[qb] : kBlock;
+    const float term = pool_term(p.dq_pool, p.pool_f32, p.q_block_coarse, qb, q_size, width, col);
+    store_grad_columns(n > 0, tmem + lane_base + 128, term, sm.out_row, p.q_out_rows, p.dq, p.dq_f32,
+                       p.f32_accumulate != 0, qb, width, col);
   }
-
-  if (n > 0) {
-    mbar_wait(&sm.dq_done, (n - 1) & 1, abort_flag, p.status, 16);
-    tc_fence_after();
-  }
-  const long long width = static_cast<long long>(p.heads) * kDim;
-  const long long col = static_cast<long long>(head) * kDim + tid;
-  const int q_size = p.q_sizes != nullptr ? p.q_sizes[qb] : kBlock;
-  const float term = pool_term(p.dq_pool, p.pool_f32, p.q_block_coarse, qb, q_size, width, col);
-  store_grad_columns(n > 0, tmem + lane_base + 128, term, sm.out_row, p.q_out_rows, p.dq, p.dq_f32,
-                     p.f32_accumulate != 0, qb, width, col);
   tc_fence_before();
   __syncthreads();
   if (warp == 0) tmem_dealloc(tmem, kDqTmemCols);
@@ -255,19 +264,22 @@ struct DkvSmem {
   uint8_t pt[kHalfTileBytes];
   uint8_t dst[kHalfTileBytes];
   long long out_row[kBlock];
-  uint64_t kv_full, qd_full[2], sp_done, dkv_done;
-  int stage_block[2];
+  uint64_t kv_full, qd_full[2], sp_done, dkv_done, sp_free, pd_ready;
   uint32_t tmem_base;
   int abort_flag;
 };
 
+// Walks the set bits of one (head, KV block) row of the query-block bitmask in ascending order.
+// Every thread that needs the sequence keeps its own cursor, so nothing is passed through
+// shared memory.
 struct MaskCursor {
   const uint32_t* words;
   int count, word;
   uint32_t bits;
+  VSA_DEVICE MaskCursor(const uint32_t* w, int c) : words(w), count(c), word(0), bits(c > 0 ? w[0] : 0u) {}
   VSA_DEVICE int next() {
     while (bits == 0) {
-      if (++word >= count) return -1;
+      if (++word >= count) return 0;
       bits = words[word];
     }
     const int bit = __ffs(bits) - 1;
@@ -288,8 +300,8 @@ __global__ void __launch_bounds__(kThreads, 2) fine_bwd_dkv_kernel(const __grid_
   }
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int kvb = blockIdx.x, head = blockIdx.y;
-  const int row = warp * 16 + (lane & 15);  // KV slot inside the block (softmax role)
-  const int half = lane >> 4;               // which 32 query columns
+  const int row = (warp & 3) * 16 + (lane & 15);  // KV slot inside the block (score math role)
+  const int half = lane >> 4;                     // which 32 query columns
   const uint32_t* mask = p.kv_mask + (static_cast<long long>(head) * p.kv_blocks + kvb) * p.mask_words;
   int n = 0;
   for (int w = 0; w < p.mask_words; ++w) n += __popc(mask[w]);
@@ -300,6 +312,8 @@ __global__ void __launch_bounds__(kThreads, 2) fine_bwd_dkv_kernel(const __grid_
     mbar_init(&sm.qd_full[1], 1);
     mbar_init(&sm.sp_done, 1);
     mbar_init(&sm.dkv_done, 1);
+    mbar_init(&sm.sp_free, kSoftmaxThreads);
+    mbar_init(&sm.pd_ready, kSoftmaxThreads);
     sm.abort_flag = 0;
     fence_barrier_init();
   }
@@ -311,118 +325,122 @@ __global__ void __launch_bounds__(kThreads, 2) fine_bwd_dkv_kernel(const __grid_
     tmem_alloc(&sm.tmem_base, kDkvTmemCols);
     tmem_relinquish();
   }
-  MaskCursor cursor{mask, p.mask_words, 0, (tid == 0 && p.mask_words > 0) ? mask[0] : 0u};
-  auto load_stage = [&](int stage, int q_block) {
-    sm.stage_block[stage] = q_block;
-    mbar_expect_tx(&sm.qd_full[stage], 2 * kTileBytes);
-    tma_load_tile(sm.q[stage], &p.q_map, &sm.qd_full[stage], head, q_block);
-    tma_load_tile(sm.d_o[stage], &p.do_map, &sm.qd_full[stage], head, q_block);
-  };
-  if (tid == 0 && n > 0) {
-    mbar_expect_tx(&sm.kv_full, 2 * kTileBytes);
-    tma_load_tile(sm.k, &p.k_map, &sm.kv_full, head, kvb);
-    tma_load_tile(sm.v, &p.v_map, &sm.kv_full, head, kvb);
-    for (int s = 0; s < 2 && s < n; ++s) load_stage(s, cursor.next());
-  }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = sm.tmem_base;
-  const uint32_t lane_base = static_cast<uint32_t>(warp * 32) << 16;
+  const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
   volatile int* abort_flag = &sm.abort_flag;
-  if (tid == 0 && n > 0) {
-    mbar_wait(&sm.kv_full, 0, abort_flag, p.status, 21);
-    mbar_wait(&sm.qd_full[0], 0, abort_flag, p.status, 22);
-    tc_fence_after();
-    issue_nt_128(tmem, sm.k, sm.q[0]);
-    issue_nt_128(tmem + 64, sm.v, sm.d_o[0]);
-    umma_commit(&sm.sp_done);
-  }
-
+  MaskCursor cursor(mask, p.mask_words);
   const int kv_size = p.kv_sizes != nullptr ? p.kv_sizes[kvb] : kBlock;
-  const bool key_live = row < kv_size;
-  const float sl2 = p.scale * kLog2e;
 
-  for (int j = 0; j < n; ++j) {
-    const int b = j & 1;
-    // LSE and delta of this thread's 32 query columns, straight from global memory (L2-resident,
-    // identical addresses across the threads of a half), issued before the MMA wait.
-    const long long stat = static_cast<long long>(head) * p.q_slots +
-                           static_cast<long long>(sm.stage_block[b]) * kBlock + half * 32;
-    float lse2[32], delta[32];
-#pragma unroll
-    for (int c = 0; c < 8; ++c) {
-      const float4 a = __ldg(reinterpret_cast<const float4*>(p.lse + stat) + c);
-      const float4 d = __ldg(reinterpret_cast<const float4*>(p.delta + stat) + c);
-      lse2[4 * c] = a.x * kLog2e, lse2[4 * c + 1] = a.y * kLog2e, lse2[4 * c + 2] = a.z * kLog2e,
-      lse2[4 * c + 3] = a.w * kLog2e;
-      delta[4 * c] = d.x, delta[4 * c + 1] = d.y, delta[4 * c + 2] = d.z, delta[4 * c + 3] = d.w;
-    }
-    mbar_wait(&sm.sp_done, j & 1, abort_flag, p.status, 23);
-    tc_fence_after();
-    uint32_t s_bits[32], dp_bits[32];
-    VSA_TMEM_LD_16x32bx2_X32(s_bits, tmem + lane_base, 32);
-    VSA_TMEM_LD_16x32bx2_X32(dp_bits, tmem + lane_base + 64, 32);
-    tmem_wait_ld();
-    uint32_t p_packed[16], ds_packed[16];
-#pragma unroll
-    for (int i = 0; i < 32; i += 2) {
-      float pr[2], ds[2];
-#pragma unroll
-      for (int e = 0; e < 2; ++e) {
-        const bool live = key_live && lse2[i + e] != -INFINITY;
-        pr[e] = live ? fast_exp2(fmaf(__uint_as_float(s_bits[i + e]), sl2, -lse2[i + e])) : 0.f;
-        ds[e] = pr[e] * (__uint_as_float(dp_bits[i + e]) - delta[i + e]) * p.scale;
-      }
-      p_packed[i >> 1] = pack_bf16(pr[0], pr[1]);
-      ds_packed[i >> 1] = pack_bf16(ds[0], ds[1]);
-    }
-    if (j > 0) {
-      // dK/dV step j-1 done: P^T / dS^T buffers and Q/dO stage b^1 are free again.
-      mbar_wait(&sm.dkv_done, (j - 1) & 1, abort_flag, p.status, 25);
+  if (warp == 4) {
+    // ------------------------------------------------------------ issuer: TMA loads and MMAs
+    if (lane == 0 && n > 0) {
+      auto load_stage = [&](int stage, int q_block) {
+        mbar_expect_tx(&sm.qd_full[stage], 2 * kTileBytes);
+        tma_load_tile(sm.q[stage], &p.q_map, &sm.qd_full[stage], head, q_block);
+        tma_load_tile(sm.d_o[stage], &p.do_map, &sm.qd_full[stage], head, q_block);
+      };
+      mbar_expect_tx(&sm.kv_full, 2 * kTileBytes);
+      tma_load_tile(sm.k, &p.k_map, &sm.kv_full, head, kvb);
+      tma_load_tile(sm.v, &p.v_map, &sm.kv_full, head, kvb);
+      for (int s = 0; s < 2 && s < n; ++s) load_stage(s, cursor.next());
+      mbar_wait(&sm.kv_full, 0, abort_flag, p.status, 21);
+      mbar_wait(&sm.qd_full[0], 0, abort_flag, p.status, 22);
       tc_fence_after();
-      if (tid == 0 && j + 1 < n) load_stage(b ^ 1, cursor.next());
-      __syncwarp();
-    }
-#pragma unroll
-    for (int c = 0; c < 4; ++c) {
-      const uint32_t off = swizzled_offset(row, half * 4 + c);
-      *reinterpret_cast<uint4*>(sm.pt + off) =
-          make_uint4(p_packed[4 * c], p_packed[4 * c + 1], p_packed[4 * c + 2], p_packed[4 * c + 3]);
-      *reinterpret_cast<uint4*>(sm.dst + off) =
-          make_uint4(ds_packed[4 * c], ds_packed[4 * c + 1], ds_packed[4 * c + 2], ds_packed[4 * c + 3]);
-    }
-    fence_proxy_async_smem();
-    tc_fence_before();
-    __syncthreads();
-    if (tid == 0) {
-      tc_fence_after();
-      issue_tn_128(tmem + 192, sm.d_o[b], sm.pt, j > 0);  // dV^T += dO^T P
-      issue_tn_128(tmem + 128, sm.q[b], sm.dst, j > 0);   // dK^T += Q^T dS
-      umma_commit(&sm.dkv_done);
-      if (j + 1 < n) {
-        mbar_wait(&sm.qd_full[b ^ 1], ((j + 1) >> 1) & 1, abort_flag, p.status, 26);
+      issue_nt_128(tmem, sm.k, sm.q[0]);
+      issue_nt_128(tmem + 64, sm.v, sm.d_o[0]);
+      umma_commit(&sm.sp_done);
+      for (int j = 0; j < n; ++j) {
+        const int b = j & 1;
+        if (j + 1 < n) {
+          mbar_wait(&sm.sp_free, j & 1, abort_flag, p.status, 28);
+          mbar_wait(&sm.qd_full[b ^ 1], ((j + 1) >> 1) & 1, abort_flag, p.status, 26);
+          tc_fence_after();
+          issue_nt_128(tmem, sm.k, sm.q[b ^ 1]);
+          issue_nt_128(tmem + 64, sm.v, sm.d_o[b ^ 1]);
+          umma_commit(&sm.sp_done);
+        }
+        mbar_wait(&sm.pd_ready, j & 1, abort_flag, p.status, 29);
         tc_fence_after();
-        issue_nt_128(tmem, sm.k, sm.q[b ^ 1]);
-        issue_nt_128(tmem + 64, sm.v, sm.d_o[b ^ 1]);
-        umma_commit(&sm.sp_done);
+        issue_tn_128(tmem + 192, sm.d_o[b], sm.pt, j > 0);  // dV^T += dO^T P
+        issue_tn_128(tmem + 128, sm.q[b], sm.dst, j > 0);   // dK^T += Q^T dS
+        umma_commit(&sm.dkv_done);
+        if (j + 2 < n) {
+          // Stage b is free once this step (the newest commit on the barrier) has read Q_j, dO_j.
+          mbar_wait(&sm.dkv_done, j & 1, abort_flag, p.status, 25);
+          load_stage(b, cursor.next());
+        }
       }
     }
-    __syncwarp();
+  } else {
+    // ------------------------------------------------------------ score math warps
+    const bool key_live = row < kv_size;
+    const float sl2 = p.scale * kLog2e;
+    for (int j = 0; j < n; ++j) {
+      // LSE and delta of this thread's 32 query columns, straight from global memory (L2-resident,
+      // identical addresses across the threads of a half), issued before the MMA wait.
+      const long long stat = static_cast<long long>(head) * p.q_slots +
+                             static_cast<long long>(cursor.next()) * kBlock + half * 32;
+      float lse2[32], delta[32];
+#pragma unroll
+      for (int c = 0; c < 8; ++c) {
+        const float4 a = __ldg(reinterpret_cast<const float4*>(p.lse + stat) + c);
+        const float4 d = __ldg(reinterpret_cast<const float4*>(p.delta + stat) + c);
+        lse2[4 * c] = a.x * kLog2e, lse2[4 * c + 1] = a.y * kLog2e, lse2[4 * c + 2] = a.z * kLog2e,
+        lse2[4 * c + 3] = a.w * kLog2e;
+        delta[4 * c] = d.x, delta[4 * c + 1] = d.y, delta[4 * c + 2] = d.z, delta[4 * c + 3] = d.w;
+      }
+      mbar_wait(&sm.sp_done, j & 1, abort_flag, p.status, 23);
+      tc_fence_after();
+      uint32_t s_bits[32], dp_bits[32];
+      VSA_TMEM_LD_16x32bx2_X32(s_bits, tmem + lane_base, 32);
+      VSA_TMEM_LD_16x32bx2_X32(dp_bits, tmem + lane_base + 64, 32);
+      tmem_wait_ld();
+      tc_fence_before();
+      mbar_arrive(&sm.sp_free);
+      uint32_t p_packed[16], ds_packed[16];
+#pragma unroll
+      for (int i = 0; i < 32; i += 2) {
+        float pr[2], ds[2];
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          const bool live = key_live && lse2[i + e] != -INFINITY;
+          pr[e] = live ? fast_exp2(fmaf(__uint_as_float(s_bits[i + e]), sl2, -lse2[i + e])) : 0.f;
+          ds[e] = pr[e] * (__uint_as_float(dp_bits[i + e]) - delta[i + e]) * p.scale;
+        }
+        p_packed[i >> 1] = pack_bf16(pr[0], pr[1]);
+        ds_packed[i >> 1] = pack_bf16(ds[0], ds[1]);
+      }
+      if (j > 0) {
+        // Step j-1 has finished reading the P^T / dS^T buffers.
+        mbar_wait(&sm.dkv_done, (j - 1) & 1, abort_flag, p.status, 25);
+      }
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        const uint32_t off = swizzled_offset(row, half * 4 + c);
+        *reinterpret_cast<uint4*>(sm.pt + off) =
+            make_uint4(p_packed[4 * c], p_packed[4 * c + 1], p_packed[4 * c + 2], p_packed[4 * c + 3]);
+        *reinterpret_cast<uint4*>(sm.dst + off) =
+            make_uint4(ds_packed[4 * c], ds_packed[4 * c + 1], ds_packed[4 * c + 2], ds_packed[4 * c + 3]);
+      }
+      fence_proxy_async_smem();
+      mbar_arrive(&sm.pd_ready);
+    }
+    if (n > 0) {
+      mbar_wait(&sm.dkv_done, (n - 1) & 1, abort_flag, p.status, 27);
+      tc_fence_after();
+    }
+    const long long width = static_cast<long long>(p.heads) * kDim;
+    const long long col = static_cast<long long>(head) * kDim + tid;
+    float term = pool_term(p.dk_pool, p.pool_f32, p.kv_block_coarse, kvb, kv_size, width, col);
+    store_grad_columns(n > 0, tmem + lane_base + 128, term, sm.out_row, p.kv_out_rows, p.dk, p.dk_f32,
+                       p.f32_accumulate != 0, kvb, width, col);
+    term = pool_term(p.dv_pool, p.pool_f32, p.kv_block_coarse, kvb, kv_size, width, col);
+    store_grad_columns(n > 0, tmem + lane_base + 192, term, sm.out_row, p.kv_out_rows, p.dv, p.dv_f32,
+                       p.f32_accumulate != 0, kvb, width, col);
   }
-
-  if (n > 0) {
-    mbar_wait(&sm.dkv_done, (n - 1) & 1, abort_flag, p.status, 27);
-    tc_fence_after();
-  }
-  const long long width = static_cast<long long>(p.heads) * kDim;
-  const long long col = static_cast<long long>(head) * kDim + tid;
-  float term = pool_term(p.dk_pool, p.pool_f32, p.kv_block_coarse, kvb, kv_size, width, col);
-  store_grad_columns(n > 0, tmem + lane_base + 128, term, sm.out_row, p.kv_out_rows, p.dk, p.dk_f32,
-                     p.f32_accumulate != 0, kvb, width, col);
-  term = pool_term(p.dv_pool, p.pool_f32, p.kv_block_coarse, kvb, kv_size, width, col);
-  store_grad_columns(n > 0, tmem + lane_base + 192, term, sm.out_row, p.kv_out_rows, p.dv, p.dv_f32,
-                     p.f32_accumulate != 0, kvb, width, col);
   tc_fence_before();
   __syncthreads();
   if (warp == 0) tmem_dealloc(tmem, kDkvTmemCols);

@@ -22,7 +22,8 @@ namespace vsa {
 
 namespace {
 
-constexpr int kThreads = 128;
+constexpr int kSoftmaxThreads = 128;  // warps 0..3: softmax and epilogue
+constexpr int kThreads = 160;         // warp 4: TMA and tcgen05.mma issue
 constexpr int kTmemCols = 128;  // S [0,64)  O^T [64,128)
 constexpr uint32_t kColO = 64;
 constexpr float kLog2e = 1.4426950408889634f;
@@ -36,7 +37,7 @@ struct FwdSmem {  // placed at a 1024-byte aligned address; every tile offset is
   float alpha[kBlock];      // per query row: factor applied to O^T when the maximum is raised
   float inv_l[kBlock];      // per query row: 1 / softmax denominator (epilogue)
   long long out_row[kBlock];
-  uint64_t q_full, k_full, v_full[2], s_done, o_done;
+  uint64_t q_full, k_full, v_full[2], s_done, o_done, s_free, p_ready;
   uint32_t tmem_base;
   int abort_flag;
 };
@@ -90,6 +91,8 @@ __global__ void __launch_bounds__(kThreads, 3) fine_fwd_kernel(const __grid_cons
     mbar_init(&sm.v_full[1], 1);
     mbar_init(&sm.s_done, 1);
     mbar_init(&sm.o_done, 1);
+    mbar_init(&sm.s_free, kSoftmaxThreads);
+    mbar_init(&sm.p_ready, kSoftmaxThreads);
     sm.abort_flag = 0;
     fence_barrier_init();
     tma_prefetch_desc(&p.q_map);
@@ -108,136 +111,143 @@ __global__ void __launch_bounds__(kThreads, 3) fine_fwd_kernel(const __grid_cons
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = sm.tmem_base;
-  const uint32_t lane_base = static_cast<uint32_t>(warp * 32) << 16;
+  const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
   volatile int* abort_flag = &sm.abort_flag;
-
-  if (tid == 0 && n > 0) {
-    mbar_expect_tx(&sm.q_full, kTileBytes);
-    tma_load_tile(sm.q, &p.q_map, &sm.q_full, head, qb);
-    mbar_expect_tx(&sm.k_full, kTileBytes);
-    tma_load_tile(sm.k, &p.k_map, &sm.k_full, head, list[0]);
-    for (int s = 0; s < 2 && s < n; ++s) {
-      mbar_expect_tx(&sm.v_full[s], kTileBytes);
-      tma_load_tile(sm.v[s], &p.v_map, &sm.v_full[s], head, list[s]);
-    }
-    mbar_wait(&sm.q_full, 0, abort_flag, p.status, 1);
-    mbar_wait(&sm.k_full, 0, abort_flag, p.status, 2);
-    tc_fence_after();
-    issue_qk(tmem, sm.q, sm.k);
-    umma_commit(&sm.s_done);
-  }
 
   const float sl2 = p.scale * kLog2e;
   float m_ref = -INFINITY;  // running reference maximum of the raw scores
   float l = 0.f;            // running sum of exp2((s - m_ref) * sl2) over this thread's columns
 
-  for (int j = 0; j < n; ++j) {
-    const int b = j & 1;
-    const int kv_block = list[j];
-    const int kv_size = p.kv_sizes != nullptr ? p.kv_sizes[kv_block] : kBlock;
-
-    mbar_wait(&sm.s_done, j & 1, abort_flag, p.status, 3);
-    tc_fence_after();
-    if (tid == 0 && j + 1 < n) {
-      // S_j is complete, so the K stage is free for the next tile.
+  if (warp == 4) {
+    // ------------------------------------------------------------ issuer: TMA loads and MMAs
+    if (lane == 0 && n > 0) {
+      mbar_expect_tx(&sm.q_full, kTileBytes);
+      tma_load_tile(sm.q, &p.q_map, &sm.q_full, head, qb);
       mbar_expect_tx(&sm.k_full, kTileBytes);
-      tma_load_tile(sm.k, &p.k_map, &sm.k_full, head, list[j + 1]);
-    }
-    __syncwarp();
-    uint32_t s_bits[32];
-    VSA_TMEM_LD_16x32bx2_X32(s_bits, tmem + lane_base, 32);
-    tmem_wait_ld();
-
-    float s[32];
-    float m_tile = -INFINITY;
-    if (kv_size < kBlock) {
-#pragma unroll
-      for (int i = 0; i < 32; ++i) s[i] = (half * 32 + i < kv_size) ? __uint_as_float(s_bits[i]) : -INFINITY;
-    } else {
-#pragma unroll
-      for (int i = 0; i < 32; ++i) s[i] = __uint_as_float(s_bits[i]);
-    }
-#pragma unroll
-    for (int i = 0; i < 32; ++i) m_tile = fmaxf(m_tile, s[i]);
-    m_tile = fmaxf(m_tile, __shfl_xor_sync(0xffffffffu, m_tile, 16));
-    const float m_new = fmaxf(m_ref, m_tile);
-    // Raise the reference maximum only when it moved by more than 2^8; both threads of a row
-    // see the same m_tile, so they decide alike.
-    const bool raise = (m_new > m_ref) && (m_ref == -INFINITY || (m_new - m_ref) * sl2 > kRescaleThreshold);
-    float alpha = 1.f;
-    if (raise) {
-      alpha = (m_ref == -INFINITY) ? 0.f : fast_exp2((m_ref - m_new) * sl2);
-      m_ref = m_new;
-    }
-    if (half == 0) sm.alpha[row] = alpha;
-    const float m_use = (m_ref == -INFINITY) ? 0.f : m_ref * sl2;
-    float row_sum = 0.f;
-    uint32_t packed[16];
-#pragma unroll
-    for (int i = 0; i < 32; i += 2) {
-      const float p0 = fast_exp2(fmaf(s[i], sl2, -m_use));
-      const float p1 = fast_exp2(fmaf(s[i + 1], sl2, -m_use));
-      packed[i >> 1] = pack_bf16(p0, p1);
-      row_sum += p0 + p1;
-    }
-    l = l * alpha + row_sum;
-
-    // PV_{j-1} must be finished before P is overwritten or O^T rescaled.
-    if (j > 0) {
-      mbar_wait(&sm.o_done, (j - 1) & 1, abort_flag, p.status, 5);
-      tc_fence_after();
-      if (tid == 0 && j + 1 < n) {
-        // V stage (j+1)&1 was last read by PV_{j-1}.
-        mbar_expect_tx(&sm.v_full[b ^ 1], kTileBytes);
-        tma_load_tile(sm.v[b ^ 1], &p.v_map, &sm.v_full[b ^ 1], head, list[j + 1]);
+      tma_load_tile(sm.k, &p.k_map, &sm.k_full, head, list[0]);
+      for (int s = 0; s < 2 && s < n; ++s) {
+        mbar_expect_tx(&sm.v_full[s], kTileBytes);
+        tma_load_tile(sm.v[s], &p.v_map, &sm.v_full[s], head, list[s]);
       }
-      __syncwarp();
-    }
-#pragma unroll
-    for (int c = 0; c < 4; ++c) {
-      uint4 v4 = make_uint4(packed[4 * c], packed[4 * c + 1], packed[4 * c + 2], packed[4 * c + 3]);
-      *reinterpret_cast<uint4*>(sm.p + swizzled_offset(row, half * 4 + c)) = v4;
-    }
-    fence_proxy_async_smem();
-    tc_fence_before();
-    const int any_raise = __syncthreads_or(raise && j > 0);
-    if (any_raise) {
-      // Rare: scale column r of O^T (lane = head dim, column = query row) by alpha[r].
+      mbar_wait(&sm.q_full, 0, abort_flag, p.status, 1);
+      mbar_wait(&sm.k_full, 0, abort_flag, p.status, 2);
       tc_fence_after();
-#pragma unroll
-      for (int c = 0; c < 2; ++c) {
-        uint32_t o_bits[32];
-        const uint32_t addr = tmem + lane_base + kColO + c * 32;
-        VSA_TMEM_LD_32x32b_X32(o_bits, addr);
-        tmem_wait_ld();
-#pragma unroll
-        for (int i = 0; i < 32; ++i)
-          o_bits[i] = __float_as_uint(__uint_as_float(o_bits[i]) * sm.alpha[c * 32 + i]);
-        VSA_TMEM_ST_32x32b_X32(o_bits, addr);
-      }
-      tmem_wait_st();
-      tc_fence_before();
-      __syncthreads();
-    }
-    if (tid == 0) {
-      tc_fence_after();
-      mbar_wait(&sm.v_full[b], (j >> 1) & 1, abort_flag, p.status, 6);
-      tc_fence_after();
-      issue_pv(tmem + kColO, sm.p, sm.v[b], j > 0);
-      umma_commit(&sm.o_done);
-      if (j + 1 < n) {
-        mbar_wait(&sm.k_full, (j + 1) & 1, abort_flag, p.status, 4);
+      issue_qk(tmem, sm.q, sm.k);
+      umma_commit(&sm.s_done);
+      for (int j = 0; j < n; ++j) {
+        const int b = j & 1;
+        // S_j complete: the single K stage is free for the next tile.
+        mbar_wait(&sm.s_done, j & 1, abort_flag, p.status, 3);
+        if (j + 1 < n) {
+          mbar_expect_tx(&sm.k_full, kTileBytes);
+          tma_load_tile(sm.k, &p.k_map, &sm.k_full, head, list[j + 1]);
+          // All softmax threads hold S_j in registers: S_{j+1} may overwrite it and runs under
+          // the softmax of tile j.
+          mbar_wait(&sm.s_free, j & 1, abort_flag, p.status, 8);
+          mbar_wait(&sm.k_full, (j + 1) & 1, abort_flag, p.status, 4);
+          tc_fence_after();
+          issue_qk(tmem, sm.q, sm.k);
+          umma_commit(&sm.s_done);
+        }
+        mbar_wait(&sm.p_ready, j & 1, abort_flag, p.status, 9);
+        if (j >= 1 && j + 1 < n) {
+          // Every softmax thread saw PV_{j-1} complete before it wrote P_j, so V stage (j+1)&1 is
+          // free.  (The o_done barrier itself must not be waited on here: once PV_j is issued it
+          // may run two phases ahead of a wait for phase j-1.)
+          mbar_expect_tx(&sm.v_full[b ^ 1], kTileBytes);
+          tma_load_tile(sm.v[b ^ 1], &p.v_map, &sm.v_full[b ^ 1], head, list[j + 1]);
+        }
+        mbar_wait(&sm.v_full[b], (j >> 1) & 1, abort_flag, p.status, 6);
         tc_fence_after();
-        issue_qk(tmem, sm.q, sm.k);
-        umma_commit(&sm.s_done);
+        issue_pv(tmem + kColO, sm.p, sm.v[b], j > 0);
+        umma_commit(&sm.o_done);
       }
     }
-    __syncwarp();
+  } else {
+    // ------------------------------------------------------------ softmax warps
+    for (int j = 0; j < n; ++j) {
+      const int kv_block = list[j];
+      const int kv_size = p.kv_sizes != nullptr ? p.kv_sizes[kv_block] : kBlock;
+
+      mbar_wait(&sm.s_done, j & 1, abort_flag, p.status, 3);
+      tc_fence_after();
+      uint32_t s_bits[32];
+      VSA_TMEM_LD_16x32bx2_X32(s_bits, tmem + lane_base, 32);
+      tmem_wait_ld();
+      tc_fence_before();
+      mbar_arrive(&sm.s_free);
+
+      float s[32];
+      float m_tile = -INFINITY;
+      if (kv_size < kBlock) {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) s[i] = (half * 32 + i < kv_size) ? __uint_as_float(s_bits[i]) : -INFINITY;
+      } else {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) s[i] = __uint_as_float(s_bits[i]);
+      }
+#pragma unroll
+      for (int i = 0; i < 32; ++i) m_tile = fmaxf(m_tile, s[i]);
+      m_tile = fmaxf(m_tile, __shfl_xor_sync(0xffffffffu, m_tile, 16));
+      const float m_new = fmaxf(m_ref, m_tile);
+      // Raise the reference maximum only when it moved by more than 2^8; both threads of a row
+      // see the same m_tile, so they decide alike.
+      const bool raise = (m_new > m_ref) && (m_ref == -INFINITY || (m_new - m_ref) * sl2 > kRescaleThreshold);
+      float alpha = 1.f;
+      if (raise) {
+        alpha = (m_ref == -INFINITY) ? 0.f : fast_exp2((m_ref - m_new) * sl2);
+        m_ref = m_new;
+      }
+      if (half == 0) sm.alpha[row] = alpha;
+      const float m_use = (m_ref == -INFINITY) ? 0.f : m_ref * sl2;
+      float row_sum = 0.f;
+      uint32_t packed[16];
+#pragma unroll
+      for (int i = 0; i < 32; i += 2) {
+        const float p0 = fast_exp2(fmaf(s[i], sl2, -m_use));
+        const float p1 = fast_exp2(fmaf(s[i + 1], sl2, -m_use));
+        packed[i >> 1] = pack_bf16(p0, p1);
+        row_sum += p0 + p1;
+      }
+      l = l * alpha + row_sum;
+
+      // PV_{j-1} must be finished before P is overwritten or O^T rescaled.
+      if (j > 0) {
+        mbar_wait(&sm.o_done, (j - 1) & 1, abort_flag, p.status, 5);
+        tc_fence_after();
+      }
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        uint4 v4 = make_uint4(packed[4 * c], packed[4 * c + 1], packed[4 * c + 2], packed[4 * c + 3]);
+        *reinterpret_cast<uint4*>(sm.p + swizzled_offset(row, half * 4 + c)) = v4;
+      }
+      fence_proxy_async_smem();
+      if (named_barrier_or(1, kSoftmaxThreads, raise && j > 0)) {
+        // Rare: scale column r of O^T (lane = head dim, column = query row) by alpha[r].
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+          uint32_t o_bits[32];
+          const uint32_t addr = tmem + lane_base + kColO + c * 32;
+          VSA_TMEM_LD_32x32b_X32(o_bits, addr);
+          tmem_wait_ld();
+#pragma unroll
+          for (int i = 0; i < 32; ++i)
+            o_bits[i] = __float_as_uint(__uint_as_float(o_bits[i]) * sm.alpha[c * 32 + i]);
+          VSA_TMEM_ST_32x32b_X32(o_bits, addr);
+        }
+        tmem_wait_st();
+        // alpha[] is rewritten next iteration: every reader must be done first.
+        named_barrier(1, kSoftmaxThreads);
+      }
+      tc_fence_before();
+      mbar_arrive(&sm.p_ready);
+    }
   }
 
   // ---------------------------------------------------------------- epilogue
-  l += __shfl_xor_sync(0xffffffffu, l, 16);
   const long long width = static_cast<long long>(p.heads) * kDim;
+  if (warp < 4) {
+  l += __shfl_xor_sync(0xffffffffu, l, 16);
   if (half == 0) {
     sm.inv_l[row] = l > 0.f ? 1.f / l : 0.f;
     const long long slot = static_cast<long long>(qb) * kBlock + row;
@@ -247,7 +257,7 @@ __global__ void __launch_bounds__(kThreads, 3) fine_fwd_kernel(const __grid_cons
     mbar_wait(&sm.o_done, (n - 1) & 1, abort_flag, p.status, 7);
     tc_fence_after();
   }
-  __syncthreads();
+  named_barrier(1, kSoftmaxThreads);
   // Thread = head dim `dim`; its 64 accumulator columns are the 64 query rows.  A warp writes 32
   // consecutive BF16 (64 bytes) of one row per store.
   const int dim = tid;
@@ -283,6 +293,7 @@ __global__ void __launch_bounds__(kThreads, 3) fine_fwd_kernel(const __grid_cons
       }
     }
   }
+  }  // softmax warps
   tc_fence_before();
   __syncthreads();
   if (warp == 0) tmem_dealloc(tmem, kTmemCols);
