@@ -27,17 +27,20 @@ EncodeTiled encode_tiled() {
   return fn;
 }
 
-// Tensor map of a BF16 [rows, heads, 128] tensor: boxes of 64 elements x 1 head x 64 rows,
-// 128-byte swizzle (the layout tcgen05 shared-memory descriptors expect).
+// Tensor map of a BF16 [rows, heads, 128] tensor, described as four dimensions
+// (64 elements, rows, heads, 2 halves of the head dim) so that ONE box of 64 x 64 x 1 x 2 brings a
+// whole 64-row tile into shared memory as [half][row][128 bytes] with the 128-byte swizzle that
+// tcgen05 shared-memory descriptors expect.
 int make_tile_map(CUtensorMap* map, const void* base, int64_t rows, int32_t heads) {
   EncodeTiled encode = encode_tiled();
   if (encode == nullptr) return vsa::kNoDriverEntry;
   if ((reinterpret_cast<uintptr_t>(base) & 15) != 0) return vsa::kBadArgument;
-  const cuuint64_t dims[3] = {vsa::kDim, static_cast<cuuint64_t>(heads), static_cast<cuuint64_t>(rows)};
-  const cuuint64_t strides[2] = {vsa::kDim * 2, static_cast<cuuint64_t>(heads) * vsa::kDim * 2};
-  const cuuint32_t box[3] = {64, 1, vsa::kBlock};
-  const cuuint32_t elem[3] = {1, 1, 1};
-  const CUresult res = encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box,
+  const cuuint64_t row_bytes = static_cast<cuuint64_t>(heads) * vsa::kDim * 2;
+  const cuuint64_t dims[4] = {64, static_cast<cuuint64_t>(rows), static_cast<cuuint64_t>(heads), 2};
+  const cuuint64_t strides[3] = {row_bytes, vsa::kDim * 2, 128};
+  const cuuint32_t box[4] = {64, vsa::kBlock, 1, 2};
+  const cuuint32_t elem[4] = {1, 1, 1, 1};
+  const CUresult res = encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), dims, strides, box,
                               elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                               CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return res == CUDA_SUCCESS ? vsa::kOk : vsa::kTensorMapError;

@@ -102,27 +102,22 @@ VSA_DEVICE void fence_barrier_init() { asm volatile("fence.mbarrier_init.release
 VSA_DEVICE void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
 // ------------------------------------------------------------------------------------------
-// TMA: one 64-element x 64-row BF16 box of a [rows, heads, 128] tensor, 128-byte swizzled.
-VSA_DEVICE void tma_load_box(void* smem_dst, const CUtensorMap* map, uint64_t* bar, int d0, int head,
-                             int row0) {
+// TMA: the tensor map views a [rows, heads, 128] BF16 tensor as (64 elements, rows, heads, 2 dim
+// halves); one box of 64 x 64 x 1 x 2 is a whole 64-row tile, stored [half][row][128 bytes] with
+// the 128-byte swizzle.
+constexpr int kHalfTileBytes = kBlock * 64 * 2;  // 64 rows x 64 BF16 = 8 KiB
+constexpr int kTileBytes = 2 * kHalfTileBytes;   // 64 rows x 128 BF16 = 16 KiB
+
+VSA_DEVICE void tma_load_tile(void* smem_dst, const CUtensorMap* map, uint64_t* bar, int head, int block) {
   asm volatile(
-      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes "
-      "[%0], [%1, {%3, %4, %5}], [%2];"
-      ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(d0),
-      "r"(head), "r"(row0)
+      "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes "
+      "[%0], [%1, {%3, %4, %5, %6}], [%2];"
+      ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(0),
+      "r"(block * kBlock), "r"(head), "r"(0)
       : "memory");
 }
 VSA_DEVICE void tma_prefetch_desc(const CUtensorMap* map) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(map)) : "memory");
-}
-
-constexpr int kHalfTileBytes = kBlock * 64 * 2;  // 64 rows x 64 BF16 = 8 KiB (one swizzle-wide box)
-constexpr int kTileBytes = 2 * kHalfTileBytes;   // 64 rows x 128 BF16 = 16 KiB
-
-// Loads the 64x128 tile of block `block`, head `head` as two boxes: [d 0..63] then [d 64..127].
-VSA_DEVICE void tma_load_tile(void* smem_dst, const CUtensorMap* map, uint64_t* bar, int head, int block) {
-  tma_load_box(smem_dst, map, bar, 0, head, block * kBlock);
-  tma_load_box(static_cast<char*>(smem_dst) + kHalfTileBytes, map, bar, 64, head, block * kBlock);
 }
 
 // ------------------------------------------------------------------------------------------
