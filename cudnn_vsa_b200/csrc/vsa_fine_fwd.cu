@@ -9,9 +9,11 @@
 // operand and P, written row-major [query][key] by the softmax threads, is the K-major B
 // operand, so nothing is transposed in shared memory.  The softmax runs on all 128 threads (two
 // threads per query row, 32 score columns each); the running maximum is raised only when it grew
-// by more than 2^8, and only then is O^T rescaled in tensor memory.  Three CTAs fit on an SM
-// (128 TMEM columns, 72 KiB of shared memory each) and hide each other's MMA -> softmax -> MMA
-// latency chain.  The epilogue writes the normalised fine output in slot order, the natural-log
+// by more than 2^8, and only then is O^T rescaled in tensor memory.  Two more warps run ahead of
+// the softmax: one issues the TMA loads, one the MMAs.  S is double-buffered in tensor memory and
+// K, V and P have two shared-memory stages each, so S_{j+1} is ready before the softmax of tile j
+// ends, the softmax of tile j+1 does not wait for the P V product of tile j, and the next tiles
+// are fetched under the current one.  Two CTAs share an SM.  The epilogue writes the normalised fine output in slot order, the natural-log
 // LSE and - when a row map is given - the merged result `fine + gate * coarse[block]` straight
 // into the caller's row order, which replaces the reference's separate restore and gate-add
 // passes (reference vsa_core.py:15-20, vsa_kernels.py:191-201, vsa.py:111-117).
@@ -23,21 +25,21 @@ namespace vsa {
 namespace {
 
 constexpr int kSoftmaxThreads = 128;  // warps 0..3: softmax and epilogue
-constexpr int kThreads = 160;         // warp 4: TMA and tcgen05.mma issue
-constexpr int kTmemCols = 128;  // S [0,64)  O^T [64,128)
-constexpr uint32_t kColO = 64;
+constexpr int kThreads = 192;         // warp 4: tcgen05.mma issue, warp 5: TMA loads
+constexpr int kTmemCols = 256;        // S0 [0,64)  S1 [64,128)  O^T [128,192)
+constexpr uint32_t kColO = 128;
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kRescaleThreshold = 8.0f;  // log2 units
 
 struct FwdSmem {  // placed at a 1024-byte aligned address; every tile offset is a multiple of 1024
   uint8_t q[kTileBytes];
-  uint8_t k[kTileBytes];
+  uint8_t k[2][kTileBytes];
   uint8_t v[2][kTileBytes];
-  uint8_t p[kHalfTileBytes];
+  uint8_t p[2][kHalfTileBytes];
   float alpha[kBlock];      // per query row: factor applied to O^T when the maximum is raised
   float inv_l[kBlock];      // per query row: 1 / softmax denominator (epilogue)
   long long out_row[kBlock];
-  uint64_t q_full, k_full, v_full[2], s_done, o_done, s_free, p_ready;
+  uint64_t q_full, k_full[2], v_full[2], s_done[2], o_done[2], p_ready[2];
   uint32_t tmem_base;
   int abort_flag;
 };
@@ -73,7 +75,7 @@ VSA_DEVICE void issue_pv(uint32_t tmem_o, const uint8_t* p, const uint8_t* v, bo
 }  // namespace
 
 template <bool kMerge>
-__global__ void __launch_bounds__(kThreads, 3) fine_fwd_kernel(const __grid_constant__ FineFwdParams p) {
+__global__ void __launch_bounds__(kThreads, 2) fine_fwd_kernel(const __grid_constant__ FineFwdParams p) {
   extern __shared__ uint8_t smem_raw[];
   FwdSmem& sm = *reinterpret_cast<FwdSmem*>(smem_raw + ((1024 - (smem_u32(smem_raw) & 1023)) & 1023));
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -86,13 +88,13 @@ __global__ void __launch_bounds__(kThreads, 3) fine_fwd_kernel(const __grid_cons
 
   if (tid == 0) {
     mbar_init(&sm.q_full, 1);
-    mbar_init(&sm.k_full, 1);
-    mbar_init(&sm.v_full[0], 1);
-    mbar_init(&sm.v_full[1], 1);
-    mbar_init(&sm.s_done, 1);
-    mbar_init(&sm.o_done, 1);
-    mbar_init(&sm.s_free, kSoftmaxThreads);
-    mbar_init(&sm.p_ready, kSoftmaxThreads);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&sm.k_full[i], 1);
+      mbar_init(&sm.v_full[i], 1);
+      mbar_init(&sm.s_done[i], 1);
+      mbar_init(&sm.o_done[i], 1);
+      mbar_init(&sm.p_ready[i], kSoftmaxThreads);
+    }
     sm.abort_flag = 0;
     fence_barrier_init();
     tma_prefetch_desc(&p.q_map);
@@ -118,64 +120,69 @@ __global__ void __launch_bounds__(kThreads, 3) fine_fwd_kernel(const __grid_cons
   float m_ref = -INFINITY;  // running reference maximum of the raw scores
   float l = 0.f;            // running sum of exp2((s - m_ref) * sl2) over this thread's columns
 
-  if (warp == 4) {
-    // ------------------------------------------------------------ issuer: TMA loads and MMAs
+  // Barrier discipline: a barrier is only ever waited on for its NEWEST commit or arrival round
+  // (a wait for an older phase could find the barrier two phases ahead and block).  That is why S,
+  // P, K and V each have one barrier per buffer.
+  if (warp == 5) {
+    // ------------------------------------------------------------ producer: TMA loads
     if (lane == 0 && n > 0) {
       mbar_expect_tx(&sm.q_full, kTileBytes);
       tma_load_tile(sm.q, &p.q_map, &sm.q_full, head, qb);
-      mbar_expect_tx(&sm.k_full, kTileBytes);
-      tma_load_tile(sm.k, &p.k_map, &sm.k_full, head, list[0]);
-      for (int s = 0; s < 2 && s < n; ++s) {
-        mbar_expect_tx(&sm.v_full[s], kTileBytes);
-        tma_load_tile(sm.v[s], &p.v_map, &sm.v_full[s], head, list[s]);
+      for (int t = 0; t < n; ++t) {
+        const int b = t & 1;
+        // K stage b was last read by S_{t-2}, V stage b by PV_{t-2}: the newest commits on
+        // s_done[b] and o_done[b] (S_t and PV_t cannot be issued before these loads land).
+        if (t >= 2) mbar_wait(&sm.s_done[b], ((t - 2) >> 1) & 1, abort_flag, p.status, 3);
+        mbar_expect_tx(&sm.k_full[b], kTileBytes);
+        tma_load_tile(sm.k[b], &p.k_map, &sm.k_full[b], head, list[t]);
+        if (t >= 2) mbar_wait(&sm.o_done[b], ((t - 2) >> 1) & 1, abort_flag, p.status, 10);
+        mbar_expect_tx(&sm.v_full[b], kTileBytes);
+        tma_load_tile(sm.v[b], &p.v_map, &sm.v_full[b], head, list[t]);
       }
+    }
+  } else if (warp == 4) {
+    // ------------------------------------------------------------ issuer: MMAs
+    if (lane == 0 && n > 0) {
       mbar_wait(&sm.q_full, 0, abort_flag, p.status, 1);
-      mbar_wait(&sm.k_full, 0, abort_flag, p.status, 2);
-      tc_fence_after();
-      issue_qk(tmem, sm.q, sm.k);
-      umma_commit(&sm.s_done);
+      for (int t = 0; t < 2 && t < n; ++t) {
+        mbar_wait(&sm.k_full[t], 0, abort_flag, p.status, 2);
+        tc_fence_after();
+        issue_qk(tmem + t * 64, sm.q, sm.k[t]);
+        umma_commit(&sm.s_done[t]);
+      }
       for (int j = 0; j < n; ++j) {
         const int b = j & 1;
-        // S_j complete: the single K stage is free for the next tile.
-        mbar_wait(&sm.s_done, j & 1, abort_flag, p.status, 3);
-        if (j + 1 < n) {
-          mbar_expect_tx(&sm.k_full, kTileBytes);
-          tma_load_tile(sm.k, &p.k_map, &sm.k_full, head, list[j + 1]);
-          // All softmax threads hold S_j in registers: S_{j+1} may overwrite it and runs under
-          // the softmax of tile j.
-          mbar_wait(&sm.s_free, j & 1, abort_flag, p.status, 8);
-          mbar_wait(&sm.k_full, (j + 1) & 1, abort_flag, p.status, 4);
-          tc_fence_after();
-          issue_qk(tmem, sm.q, sm.k);
-          umma_commit(&sm.s_done);
-        }
-        mbar_wait(&sm.p_ready, j & 1, abort_flag, p.status, 9);
-        if (j >= 1 && j + 1 < n) {
-          // Every softmax thread saw PV_{j-1} complete before it wrote P_j, so V stage (j+1)&1 is
-          // free.  (The o_done barrier itself must not be waited on here: once PV_j is issued it
-          // may run two phases ahead of a wait for phase j-1.)
-          mbar_expect_tx(&sm.v_full[b ^ 1], kTileBytes);
-          tma_load_tile(sm.v[b ^ 1], &p.v_map, &sm.v_full[b ^ 1], head, list[j + 1]);
-        }
+        // P_j written: every softmax thread has S_j in registers.
+        mbar_wait(&sm.p_ready[b], (j >> 1) & 1, abort_flag, p.status, 9);
         mbar_wait(&sm.v_full[b], (j >> 1) & 1, abort_flag, p.status, 6);
         tc_fence_after();
-        issue_pv(tmem + kColO, sm.p, sm.v[b], j > 0);
-        umma_commit(&sm.o_done);
+        issue_pv(tmem + kColO, sm.p[b], sm.v[b], j > 0);
+        umma_commit(&sm.o_done[b]);
+        if (j + 2 < n) {
+          // S buffer b is free (S_j is in registers): S_{j+2} runs under the next softmax.
+          mbar_wait(&sm.k_full[b], ((j + 2) >> 1) & 1, abort_flag, p.status, 4);
+          tc_fence_after();
+          issue_qk(tmem + b * 64, sm.q, sm.k[b]);
+          umma_commit(&sm.s_done[b]);
+        }
       }
     }
   } else {
     // ------------------------------------------------------------ softmax warps
+    // The valid length of tile j comes from two dependent global loads (list, then sizes);
+    // they are issued two and one iterations ahead so their latency never sits in the loop.
+    int next_block = n > 1 ? list[1] : 0;
+    int next_size = (n > 0 && p.kv_sizes != nullptr) ? p.kv_sizes[list[0]] : kBlock;
     for (int j = 0; j < n; ++j) {
-      const int kv_block = list[j];
-      const int kv_size = p.kv_sizes != nullptr ? p.kv_sizes[kv_block] : kBlock;
+      const int kv_size = next_size;
+      if (p.kv_sizes != nullptr && j + 1 < n) next_size = p.kv_sizes[next_block];
+      if (j + 2 < n) next_block = list[j + 2];
 
-      mbar_wait(&sm.s_done, j & 1, abort_flag, p.status, 3);
+      mbar_wait(&sm.s_done[j & 1], (j >> 1) & 1, abort_flag, p.status, 3);
       tc_fence_after();
       uint32_t s_bits[32];
-      VSA_TMEM_LD_16x32bx2_X32(s_bits, tmem + lane_base, 32);
+      VSA_TMEM_LD_16x32bx2_X32(s_bits, tmem + lane_base + (j & 1) * 64, 32);
       tmem_wait_ld();
-      tc_fence_before();
-      mbar_arrive(&sm.s_free);
 
       float s[32];
       float m_tile = -INFINITY;
@@ -186,8 +193,13 @@ __global__ void __launch_bounds__(kThreads, 3) fine_fwd_kernel(const __grid_cons
 #pragma unroll
         for (int i = 0; i < 32; ++i) s[i] = __uint_as_float(s_bits[i]);
       }
+      {
+        // Four independent chains keep the dependent-latency path short.
+        float m4[4] = {s[0], s[1], s[2], s[3]};
 #pragma unroll
-      for (int i = 0; i < 32; ++i) m_tile = fmaxf(m_tile, s[i]);
+        for (int i = 4; i < 32; ++i) m4[i & 3] = fmaxf(m4[i & 3], s[i]);
+        m_tile = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
+      }
       m_tile = fmaxf(m_tile, __shfl_xor_sync(0xffffffffu, m_tile, 16));
       const float m_new = fmaxf(m_ref, m_tile);
       // Raise the reference maximum only when it moved by more than 2^8; both threads of a row
@@ -200,30 +212,30 @@ __global__ void __launch_bounds__(kThreads, 3) fine_fwd_kernel(const __grid_cons
       }
       if (half == 0) sm.alpha[row] = alpha;
       const float m_use = (m_ref == -INFINITY) ? 0.f : m_ref * sl2;
-      float row_sum = 0.f;
+      float sum4[4] = {0.f, 0.f, 0.f, 0.f};
       uint32_t packed[16];
 #pragma unroll
       for (int i = 0; i < 32; i += 2) {
         const float p0 = fast_exp2(fmaf(s[i], sl2, -m_use));
         const float p1 = fast_exp2(fmaf(s[i + 1], sl2, -m_use));
         packed[i >> 1] = pack_bf16(p0, p1);
-        row_sum += p0 + p1;
+        sum4[(i >> 1) & 3] += p0 + p1;
       }
-      l = l * alpha + row_sum;
+      l = l * alpha + ((sum4[0] + sum4[1]) + (sum4[2] + sum4[3]));
 
-      // PV_{j-1} must be finished before P is overwritten or O^T rescaled.
-      if (j > 0) {
-        mbar_wait(&sm.o_done, (j - 1) & 1, abort_flag, p.status, 5);
-        tc_fence_after();
-      }
+      // P buffer j&1 was last read by PV_{j-2}, the newest commit on o_done[j&1].
+      if (j > 1) mbar_wait(&sm.o_done[j & 1], ((j - 2) >> 1) & 1, abort_flag, p.status, 5);
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
         uint4 v4 = make_uint4(packed[4 * c], packed[4 * c + 1], packed[4 * c + 2], packed[4 * c + 3]);
-        *reinterpret_cast<uint4*>(sm.p + swizzled_offset(row, half * 4 + c)) = v4;
+        *reinterpret_cast<uint4*>(sm.p[j & 1] + swizzled_offset(row, half * 4 + c)) = v4;
       }
       fence_proxy_async_smem();
       if (named_barrier_or(1, kSoftmaxThreads, raise && j > 0)) {
-        // Rare: scale column r of O^T (lane = head dim, column = query row) by alpha[r].
+        // Rare: scale column r of O^T (lane = head dim, column = query row) by alpha[r], once
+        // PV_{j-1} (the newest commit on o_done[(j-1)&1]) has finished.
+        mbar_wait(&sm.o_done[(j - 1) & 1], ((j - 1) >> 1) & 1, abort_flag, p.status, 11);
+        tc_fence_after();
 #pragma unroll
         for (int c = 0; c < 2; ++c) {
           uint32_t o_bits[32];
@@ -240,7 +252,7 @@ __global__ void __launch_bounds__(kThreads, 3) fine_fwd_kernel(const __grid_cons
         named_barrier(1, kSoftmaxThreads);
       }
       tc_fence_before();
-      mbar_arrive(&sm.p_ready);
+      mbar_arrive(&sm.p_ready[j & 1]);
     }
   }
 
@@ -254,7 +266,7 @@ __global__ void __launch_bounds__(kThreads, 3) fine_fwd_kernel(const __grid_cons
     p.lse[static_cast<long long>(head) * p.q_slots + slot] = l > 0.f ? m_ref * p.scale + logf(l) : -INFINITY;
   }
   if (n > 0) {
-    mbar_wait(&sm.o_done, (n - 1) & 1, abort_flag, p.status, 7);
+    mbar_wait(&sm.o_done[(n - 1) & 1], ((n - 1) >> 1) & 1, abort_flag, p.status, 7);
     tc_fence_after();
   }
   named_barrier(1, kSoftmaxThreads);
