@@ -36,10 +36,10 @@ struct FwdSmem {  // placed at a 1024-byte aligned address; every tile offset is
   uint8_t k[2][kTileBytes];
   uint8_t v[2][kTileBytes];
   uint8_t p[2][kHalfTileBytes];
-  float alpha[kBlock];      // per query row: factor applied to O^T when the maximum is raised
+  float alpha[2][kBlock];   // per tile of the pair and query row: factor applied when the maximum is raised
   float inv_l[kBlock];      // per query row: 1 / softmax denominator (epilogue)
   long long out_row[kBlock];
-  uint64_t q_full, k_full[2], v_full[2], s_done[2], o_done[2], p_ready[2];
+  uint64_t q_full, k_full[2], v_full[2], s_done, o_done, s_free, p_ready;
   uint32_t tmem_base;
   int abort_flag;
 };
@@ -91,10 +91,11 @@ __global__ void __launch_bounds__(kThreads, 2) fine_fwd_kernel(const __grid_cons
     for (int i = 0; i < 2; ++i) {
       mbar_init(&sm.k_full[i], 1);
       mbar_init(&sm.v_full[i], 1);
-      mbar_init(&sm.s_done[i], 1);
-      mbar_init(&sm.o_done[i], 1);
-      mbar_init(&sm.p_ready[i], kSoftmaxThreads);
     }
+    mbar_init(&sm.s_done, 1);
+    mbar_init(&sm.o_done, 1);
+    mbar_init(&sm.s_free, kSoftmaxThreads);
+    mbar_init(&sm.p_ready, kSoftmaxThreads);
     sm.abort_flag = 0;
     fence_barrier_init();
     tma_prefetch_desc(&p.q_map);
@@ -120,121 +121,170 @@ __global__ void __launch_bounds__(kThreads, 2) fine_fwd_kernel(const __grid_cons
   float m_ref = -INFINITY;  // running reference maximum of the raw scores
   float l = 0.f;            // running sum of exp2((s - m_ref) * sl2) over this thread's columns
 
-  // Barrier discipline: a barrier is only ever waited on for its NEWEST commit or arrival round
-  // (a wait for an older phase could find the barrier two phases ahead and block).  That is why S,
-  // P, K and V each have one barrier per buffer.
+  // Tiles are processed two at a time ("pair" i = tiles 2i and 2i+1): the softmax warps pull both
+  // score tiles into registers, release the S buffers, and pay for one fence, one consensus
+  // barrier and one arrival per pair.  Barrier discipline: a barrier is only ever waited on for its
+  // NEWEST commit or arrival round (a wait for an older phase could find the barrier two phases
+  // ahead and block); every producer/consumer edge below is ordered so that this holds.
+  const int pairs = (n + 1) >> 1;
   if (warp == 5) {
     // ------------------------------------------------------------ producer: TMA loads
     if (lane == 0 && n > 0) {
       mbar_expect_tx(&sm.q_full, kTileBytes);
       tma_load_tile(sm.q, &p.q_map, &sm.q_full, head, qb);
-      for (int t = 0; t < n; ++t) {
-        const int b = t & 1;
-        // K stage b was last read by S_{t-2}, V stage b by PV_{t-2}: the newest commits on
-        // s_done[b] and o_done[b] (S_t and PV_t cannot be issued before these loads land).
-        if (t >= 2) mbar_wait(&sm.s_done[b], ((t - 2) >> 1) & 1, abort_flag, p.status, 3);
-        mbar_expect_tx(&sm.k_full[b], kTileBytes);
-        tma_load_tile(sm.k[b], &p.k_map, &sm.k_full[b], head, list[t]);
-        if (t >= 2) mbar_wait(&sm.o_done[b], ((t - 2) >> 1) & 1, abort_flag, p.status, 10);
-        mbar_expect_tx(&sm.v_full[b], kTileBytes);
-        tma_load_tile(sm.v[b], &p.v_map, &sm.v_full[b], head, list[t]);
+      auto load_k = [&](int i) {
+        for (int t = 0; t < 2 && 2 * i + t < n; ++t) {
+          mbar_expect_tx(&sm.k_full[t], kTileBytes);
+          tma_load_tile(sm.k[t], &p.k_map, &sm.k_full[t], head, list[2 * i + t]);
+        }
+      };
+      load_k(0);
+      for (int i = 0; i < pairs; ++i) {
+        // The S products of pair i finish before the P V products of pair i-1 (they are issued
+        // first), so K of pair i+1 is fetched before V of pair i: each load starts as soon as its
+        // stage is free.  Both waits are for the newest commit on their barrier (pair i+1 cannot
+        // be issued before these loads land).
+        if (i + 1 < pairs) {
+          mbar_wait(&sm.s_done, i & 1, abort_flag, p.status, 3);
+          load_k(i + 1);
+        }
+        if (i > 0) mbar_wait(&sm.o_done, (i - 1) & 1, abort_flag, p.status, 10);
+        for (int t = 0; t < 2 && 2 * i + t < n; ++t) {
+          mbar_expect_tx(&sm.v_full[t], kTileBytes);
+          tma_load_tile(sm.v[t], &p.v_map, &sm.v_full[t], head, list[2 * i + t]);
+        }
       }
     }
   } else if (warp == 4) {
     // ------------------------------------------------------------ issuer: MMAs
     if (lane == 0 && n > 0) {
       mbar_wait(&sm.q_full, 0, abort_flag, p.status, 1);
-      for (int t = 0; t < 2 && t < n; ++t) {
-        mbar_wait(&sm.k_full[t], 0, abort_flag, p.status, 2);
-        tc_fence_after();
-        issue_qk(tmem + t * 64, sm.q, sm.k[t]);
-        umma_commit(&sm.s_done[t]);
-      }
-      for (int j = 0; j < n; ++j) {
-        const int b = j & 1;
-        // P_j written: every softmax thread has S_j in registers.
-        mbar_wait(&sm.p_ready[b], (j >> 1) & 1, abort_flag, p.status, 9);
-        mbar_wait(&sm.v_full[b], (j >> 1) & 1, abort_flag, p.status, 6);
-        tc_fence_after();
-        issue_pv(tmem + kColO, sm.p[b], sm.v[b], j > 0);
-        umma_commit(&sm.o_done[b]);
-        if (j + 2 < n) {
-          // S buffer b is free (S_j is in registers): S_{j+2} runs under the next softmax.
-          mbar_wait(&sm.k_full[b], ((j + 2) >> 1) & 1, abort_flag, p.status, 4);
+      for (int i = 0; i < pairs; ++i) {
+        const int count = (2 * i + 1 < n) ? 2 : 1;
+        // S buffers are free once every softmax thread holds pair i-1 in registers.
+        if (i > 0) mbar_wait(&sm.s_free, (i - 1) & 1, abort_flag, p.status, 8);
+        for (int t = 0; t < count; ++t) {
+          mbar_wait(&sm.k_full[t], i & 1, abort_flag, p.status, 2);
           tc_fence_after();
-          issue_qk(tmem + b * 64, sm.q, sm.k[b]);
-          umma_commit(&sm.s_done[b]);
+          issue_qk(tmem + t * 64, sm.q, sm.k[t]);
+        }
+        umma_commit(&sm.s_done);
+        if (i > 0) {
+          // P of pair i-1 is written; its P V products follow the S products of pair i so that
+          // the next softmax never waits for them.
+          const int prev = (2 * i - 1 < n) ? 2 : 1;
+          mbar_wait(&sm.p_ready, (i - 1) & 1, abort_flag, p.status, 9);
+          for (int t = 0; t < prev; ++t) {
+            mbar_wait(&sm.v_full[t], (i - 1) & 1, abort_flag, p.status, 6);
+            tc_fence_after();
+            issue_pv(tmem + kColO, sm.p[t], sm.v[t], i > 1 || t > 0);
+          }
+          umma_commit(&sm.o_done);
         }
       }
+      const int last = pairs - 1, count = (2 * last + 1 < n) ? 2 : 1;
+      mbar_wait(&sm.p_ready, last & 1, abort_flag, p.status, 9);
+      for (int t = 0; t < count; ++t) {
+        mbar_wait(&sm.v_full[t], last & 1, abort_flag, p.status, 6);
+        tc_fence_after();
+        issue_pv(tmem + kColO, sm.p[t], sm.v[t], last > 0 || t > 0);
+      }
+      umma_commit(&sm.o_done);
     }
   } else {
     // ------------------------------------------------------------ softmax warps
-    // The valid length of tile j comes from two dependent global loads (list, then sizes);
-    // they are issued two and one iterations ahead so their latency never sits in the loop.
-    int next_block = n > 1 ? list[1] : 0;
-    int next_size = (n > 0 && p.kv_sizes != nullptr) ? p.kv_sizes[list[0]] : kBlock;
-    for (int j = 0; j < n; ++j) {
-      const int kv_size = next_size;
-      if (p.kv_sizes != nullptr && j + 1 < n) next_size = p.kv_sizes[next_block];
-      if (j + 2 < n) next_block = list[j + 2];
-
-      mbar_wait(&sm.s_done[j & 1], (j >> 1) & 1, abort_flag, p.status, 3);
+    // The valid length of a tile comes from two dependent global loads (list, then sizes); they
+    // are issued one pair ahead so their latency never sits in the loop.
+    int size_next[2] = {kBlock, kBlock};
+    if (p.kv_sizes != nullptr) {
+      if (n > 0) size_next[0] = p.kv_sizes[list[0]];
+      if (n > 1) size_next[1] = p.kv_sizes[list[1]];
+    }
+    for (int i = 0; i < pairs; ++i) {
+      const int count = (2 * i + 1 < n) ? 2 : 1;
+      const int kv_size[2] = {size_next[0], size_next[1]};
+      if (p.kv_sizes != nullptr) {
+        if (2 * i + 2 < n) size_next[0] = p.kv_sizes[list[2 * i + 2]];
+        if (2 * i + 3 < n) size_next[1] = p.kv_sizes[list[2 * i + 3]];
+      }
+      mbar_wait(&sm.s_done, i & 1, abort_flag, p.status, 3);
       tc_fence_after();
-      uint32_t s_bits[32];
-      VSA_TMEM_LD_16x32bx2_X32(s_bits, tmem + lane_base + (j & 1) * 64, 32);
+      uint32_t s_bits[2][32];
+      VSA_TMEM_LD_16x32bx2_X32(s_bits[0], tmem + lane_base, 32);
+      if (count == 2) VSA_TMEM_LD_16x32bx2_X32(s_bits[1], tmem + lane_base + 64, 32);
       tmem_wait_ld();
+      tc_fence_before();
+      mbar_arrive(&sm.s_free);
 
-      float s[32];
-      float m_tile = -INFINITY;
-      if (kv_size < kBlock) {
+      bool raise_any = false;
+      uint32_t packed[2][16];
 #pragma unroll
-        for (int i = 0; i < 32; ++i) s[i] = (half * 32 + i < kv_size) ? __uint_as_float(s_bits[i]) : -INFINITY;
-      } else {
+      for (int t = 0; t < 2; ++t) {
+        if (t < count) {
+          float s[32];
+          if (kv_size[t] < kBlock) {
 #pragma unroll
-        for (int i = 0; i < 32; ++i) s[i] = __uint_as_float(s_bits[i]);
+            for (int e = 0; e < 32; ++e)
+              s[e] = (half * 32 + e < kv_size[t]) ? __uint_as_float(s_bits[t][e]) : -INFINITY;
+          } else {
+#pragma unroll
+            for (int e = 0; e < 32; ++e) s[e] = __uint_as_float(s_bits[t][e]);
+          }
+          // Four independent chains keep the dependent-latency path short.
+          float m4[4] = {s[0], s[1], s[2], s[3]};
+#pragma unroll
+          for (int e = 4; e < 32; ++e) m4[e & 3] = fmaxf(m4[e & 3], s[e]);
+          float m_tile = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
+          m_tile = fmaxf(m_tile, __shfl_xor_sync(0xffffffffu, m_tile, 16));
+          const float m_new = fmaxf(m_ref, m_tile);
+          // Raise the reference maximum only when it moved by more than 2^8; both threads of a
+          // row see the same m_tile, so they decide alike.
+          const bool raise = (m_new > m_ref) && (m_ref == -INFINITY || (m_new - m_ref) * sl2 > kRescaleThreshold);
+          float alpha = 1.f;
+          if (raise) {
+            alpha = (m_ref == -INFINITY) ? 0.f : fast_exp2((m_ref - m_new) * sl2);
+            m_ref = m_new;
+          }
+          // alpha[t][row]: factor for everything accumulated before tile t of this pair.
+          if (half == 0) sm.alpha[t][row] = alpha;
+          raise_any |= raise && (i > 0 || t > 0);
+          if (t == 1 && raise) {
+            // Tile 0 of this pair was scaled with the old reference: bring its P up to date.
+#pragma unroll
+            for (int e = 0; e < 16; ++e) {
+              const float2 f = unpack_bf16(packed[0][e]);
+              packed[0][e] = pack_bf16(f.x * alpha, f.y * alpha);
+            }
+          }
+          const float m_use = (m_ref == -INFINITY) ? 0.f : m_ref * sl2;
+          float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+          for (int e = 0; e < 32; e += 2) {
+            const float p0 = fast_exp2(fmaf(s[e], sl2, -m_use));
+            const float p1 = fast_exp2(fmaf(s[e + 1], sl2, -m_use));
+            packed[t][e >> 1] = pack_bf16(p0, p1);
+            sum4[(e >> 1) & 3] += p0 + p1;
+          }
+          l = l * alpha + ((sum4[0] + sum4[1]) + (sum4[2] + sum4[3]));
+        } else if (half == 0) {
+          sm.alpha[t][row] = 1.f;
+        }
       }
-      {
-        // Four independent chains keep the dependent-latency path short.
-        float m4[4] = {s[0], s[1], s[2], s[3]};
+      // P buffers were last read by the P V products of pair i-1, the newest commit on o_done.
+      if (i > 0) mbar_wait(&sm.o_done, (i - 1) & 1, abort_flag, p.status, 5);
 #pragma unroll
-        for (int i = 4; i < 32; ++i) m4[i & 3] = fmaxf(m4[i & 3], s[i]);
-        m_tile = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
-      }
-      m_tile = fmaxf(m_tile, __shfl_xor_sync(0xffffffffu, m_tile, 16));
-      const float m_new = fmaxf(m_ref, m_tile);
-      // Raise the reference maximum only when it moved by more than 2^8; both threads of a row
-      // see the same m_tile, so they decide alike.
-      const bool raise = (m_new > m_ref) && (m_ref == -INFINITY || (m_new - m_ref) * sl2 > kRescaleThreshold);
-      float alpha = 1.f;
-      if (raise) {
-        alpha = (m_ref == -INFINITY) ? 0.f : fast_exp2((m_ref - m_new) * sl2);
-        m_ref = m_new;
-      }
-      if (half == 0) sm.alpha[row] = alpha;
-      const float m_use = (m_ref == -INFINITY) ? 0.f : m_ref * sl2;
-      float sum4[4] = {0.f, 0.f, 0.f, 0.f};
-      uint32_t packed[16];
+      for (int t = 0; t < 2; ++t) {
+        if (t < count) {
 #pragma unroll
-      for (int i = 0; i < 32; i += 2) {
-        const float p0 = fast_exp2(fmaf(s[i], sl2, -m_use));
-        const float p1 = fast_exp2(fmaf(s[i + 1], sl2, -m_use));
-        packed[i >> 1] = pack_bf16(p0, p1);
-        sum4[(i >> 1) & 3] += p0 + p1;
-      }
-      l = l * alpha + ((sum4[0] + sum4[1]) + (sum4[2] + sum4[3]));
-
-      // P buffer j&1 was last read by PV_{j-2}, the newest commit on o_done[j&1].
-      if (j > 1) mbar_wait(&sm.o_done[j & 1], ((j - 2) >> 1) & 1, abort_flag, p.status, 5);
-#pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        uint4 v4 = make_uint4(packed[4 * c], packed[4 * c + 1], packed[4 * c + 2], packed[4 * c + 3]);
-        *reinterpret_cast<uint4*>(sm.p[j & 1] + swizzled_offset(row, half * 4 + c)) = v4;
+          for (int c = 0; c < 4; ++c)
+            *reinterpret_cast<uint4*>(sm.p[t] + swizzled_offset(row, half * 4 + c)) =
+                make_uint4(packed[t][4 * c], packed[t][4 * c + 1], packed[t][4 * c + 2], packed[t][4 * c + 3]);
+        }
       }
       fence_proxy_async_smem();
-      if (named_barrier_or(1, kSoftmaxThreads, raise && j > 0)) {
-        // Rare: scale column r of O^T (lane = head dim, column = query row) by alpha[r], once
-        // PV_{j-1} (the newest commit on o_done[(j-1)&1]) has finished.
-        mbar_wait(&sm.o_done[(j - 1) & 1], ((j - 1) >> 1) & 1, abort_flag, p.status, 11);
+      if (named_barrier_or(1, kSoftmaxThreads, raise_any)) {
+        // Rare: scale column r of O^T (lane = head dim, column = query row) by the factors of
+        // both tiles.  O^T is stable here: the P V products of pair i-1 are complete.
         tc_fence_after();
 #pragma unroll
         for (int c = 0; c < 2; ++c) {
@@ -243,8 +293,8 @@ __global__ void __launch_bounds__(kThreads, 2) fine_fwd_kernel(const __grid_cons
           VSA_TMEM_LD_32x32b_X32(o_bits, addr);
           tmem_wait_ld();
 #pragma unroll
-          for (int i = 0; i < 32; ++i)
-            o_bits[i] = __float_as_uint(__uint_as_float(o_bits[i]) * sm.alpha[c * 32 + i]);
+          for (int e = 0; e < 32; ++e)
+            o_bits[e] = __float_as_uint(__uint_as_float(o_bits[e]) * (sm.alpha[0][c * 32 + e] * sm.alpha[1][c * 32 + e]));
           VSA_TMEM_ST_32x32b_X32(o_bits, addr);
         }
         tmem_wait_st();
@@ -252,7 +302,7 @@ __global__ void __launch_bounds__(kThreads, 2) fine_fwd_kernel(const __grid_cons
         named_barrier(1, kSoftmaxThreads);
       }
       tc_fence_before();
-      mbar_arrive(&sm.p_ready[j & 1]);
+      mbar_arrive(&sm.p_ready);
     }
   }
 
@@ -266,7 +316,7 @@ __global__ void __launch_bounds__(kThreads, 2) fine_fwd_kernel(const __grid_cons
     p.lse[static_cast<long long>(head) * p.q_slots + slot] = l > 0.f ? m_ref * p.scale + logf(l) : -INFINITY;
   }
   if (n > 0) {
-    mbar_wait(&sm.o_done[(n - 1) & 1], ((n - 1) >> 1) & 1, abort_flag, p.status, 7);
+    mbar_wait(&sm.o_done, (pairs - 1) & 1, abort_flag, p.status, 7);
     tc_fence_after();
   }
   named_barrier(1, kSoftmaxThreads);
