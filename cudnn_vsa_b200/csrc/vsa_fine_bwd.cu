@@ -4,7 +4,8 @@
 //               S = Q K^T, dP = dO V^T, dS = P * (dP - delta) * scale, dQ^T += K^T dS^T.
 //   dK/dV kernel one CTA per (KV block, head), walks the query blocks that list this KV block
 //               (a per-call bitmask built by build_kv_mask_kernel):
-//               S^T = K Q^T, dP^T = V dO^T, dV^T += dO^T P, dK^T += Q^T dS.
+//               S = Q K^T, dP = dO V^T (query rows on the lanes, as in the dQ kernel, so each
+//               thread needs one LSE and one delta), dV^T += dO^T P, dK^T += Q^T dS.
 //
 // The 64 x 64 score products run with M = 64; the three "x 128-wide" gradient products are kept
 // transposed (head dim on the M axis) so that they run with M = 128, the tensor core's full-rate
@@ -51,6 +52,18 @@ VSA_DEVICE void issue_tn_128(uint32_t tmem_d, const uint8_t* a, const uint8_t* b
   for (int ks = 0; ks < 4; ++ks) {
     umma_ss(tmem_d, umma_smem_desc(smem_u32(a) + ks * 2048, kHalfTileBytes, 1024),
             umma_smem_desc(smem_u32(b) + ks * 32, 16, 1024), idesc, accumulate || ks > 0);
+  }
+}
+
+// D^T[128 x 64] (+)= A^T B with A a row-major [64 rows][128 dims] tile read MN-major and B a
+// row-major [64 rows][64] BF16 tile read MN-major as well (rows of both are the K index):
+// dV^T = dO^T P and dK^T = Q^T dS with P, dS stored [query][key].
+VSA_DEVICE void issue_tt_128(uint32_t tmem_d, const uint8_t* a, const uint8_t* b, bool accumulate) {
+  constexpr uint32_t idesc = umma_idesc(128, 64, 1, 1);
+#pragma unroll
+  for (int ks = 0; ks < 4; ++ks) {
+    umma_ss(tmem_d, umma_smem_desc(smem_u32(a) + ks * 2048, kHalfTileBytes, 1024),
+            umma_smem_desc(smem_u32(b) + ks * 2048, kHalfTileBytes, 1024), idesc, accumulate || ks > 0);
   }
 }
 
@@ -300,8 +313,8 @@ __global__ void __launch_bounds__(kThreads, 2) fine_bwd_dkv_kernel(const __grid_
   }
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int kvb = blockIdx.x, head = blockIdx.y;
-  const int row = (warp & 3) * 16 + (lane & 15);  // KV slot inside the block (score math role)
-  const int half = lane >> 4;                     // which 32 query columns
+  const int row = (warp & 3) * 16 + (lane & 15);  // query row inside the current block (score math role)
+  const int half = lane >> 4;                     // which 32 key columns
   const uint32_t* mask = p.kv_mask + (static_cast<long long>(head) * p.kv_blocks + kvb) * p.mask_words;
   int n = 0;
   for (int w = 0; w < p.mask_words; ++w) n += __popc(mask[w]);
@@ -349,8 +362,8 @@ __global__ void __launch_bounds__(kThreads, 2) fine_bwd_dkv_kernel(const __grid_
       mbar_wait(&sm.kv_full, 0, abort_flag, p.status, 21);
       mbar_wait(&sm.qd_full[0], 0, abort_flag, p.status, 22);
       tc_fence_after();
-      issue_nt_128(tmem, sm.k, sm.q[0]);
-      issue_nt_128(tmem + 64, sm.v, sm.d_o[0]);
+      issue_nt_128(tmem, sm.q[0], sm.k);
+      issue_nt_128(tmem + 64, sm.d_o[0], sm.v);
       umma_commit(&sm.sp_done);
       for (int j = 0; j < n; ++j) {
         const int b = j & 1;
@@ -358,14 +371,14 @@ __global__ void __launch_bounds__(kThreads, 2) fine_bwd_dkv_kernel(const __grid_
           mbar_wait(&sm.sp_free, j & 1, abort_flag, p.status, 28);
           mbar_wait(&sm.qd_full[b ^ 1], ((j + 1) >> 1) & 1, abort_flag, p.status, 26);
           tc_fence_after();
-          issue_nt_128(tmem, sm.k, sm.q[b ^ 1]);
-          issue_nt_128(tmem + 64, sm.v, sm.d_o[b ^ 1]);
+          issue_nt_128(tmem, sm.q[b ^ 1], sm.k);
+          issue_nt_128(tmem + 64, sm.d_o[b ^ 1], sm.v);
           umma_commit(&sm.sp_done);
         }
         mbar_wait(&sm.pd_ready, j & 1, abort_flag, p.status, 29);
         tc_fence_after();
-        issue_tn_128(tmem + 192, sm.d_o[b], sm.pt, j > 0);  // dV^T += dO^T P
-        issue_tn_128(tmem + 128, sm.q[b], sm.dst, j > 0);   // dK^T += Q^T dS
+        issue_tt_128(tmem + 192, sm.d_o[b], sm.pt, j > 0);  // dV^T += dO^T P
+        issue_tt_128(tmem + 128, sm.q[b], sm.dst, j > 0);   // dK^T += Q^T dS
         umma_commit(&sm.dkv_done);
         if (j + 2 < n) {
           // Stage b is free once this step (the newest commit on the barrier) has read Q_j, dO_j.
@@ -376,21 +389,21 @@ __global__ void __launch_bounds__(kThreads, 2) fine_bwd_dkv_kernel(const __grid_
     }
   } else {
     // ------------------------------------------------------------ score math warps
-    const bool key_live = row < kv_size;
     const float sl2 = p.scale * kLog2e;
+    const long long head_stats = static_cast<long long>(head) * p.q_slots + row;
+    // LSE and delta of this thread's query row, fetched one tile ahead.
+    float lse_next = 0.f, delta_next = 0.f;
+    if (n > 0) {
+      const long long at = head_stats + static_cast<long long>(cursor.next()) * kBlock;
+      lse_next = p.lse[at];
+      delta_next = p.delta[at];
+    }
     for (int j = 0; j < n; ++j) {
-      // LSE and delta of this thread's 32 query columns, straight from global memory (L2-resident,
-      // identical addresses across the threads of a half), issued before the MMA wait.
-      const long long stat = static_cast<long long>(head) * p.q_slots +
-                             static_cast<long long>(cursor.next()) * kBlock + half * 32;
-      float lse2[32], delta[32];
-#pragma unroll
-      for (int c = 0; c < 8; ++c) {
-        const float4 a = __ldg(reinterpret_cast<const float4*>(p.lse + stat) + c);
-        const float4 d = __ldg(reinterpret_cast<const float4*>(p.delta + stat) + c);
-        lse2[4 * c] = a.x * kLog2e, lse2[4 * c + 1] = a.y * kLog2e, lse2[4 * c + 2] = a.z * kLog2e,
-        lse2[4 * c + 3] = a.w * kLog2e;
-        delta[4 * c] = d.x, delta[4 * c + 1] = d.y, delta[4 * c + 2] = d.z, delta[4 * c + 3] = d.w;
+      const float lse2 = lse_next * kLog2e, delta = delta_next;
+      if (j + 1 < n) {
+        const long long at = head_stats + static_cast<long long>(cursor.next()) * kBlock;
+        lse_next = p.lse[at];
+        delta_next = p.delta[at];
       }
       mbar_wait(&sm.sp_done, j & 1, abort_flag, p.status, 23);
       tc_fence_after();
@@ -400,15 +413,16 @@ __global__ void __launch_bounds__(kThreads, 2) fine_bwd_dkv_kernel(const __grid_
       tmem_wait_ld();
       tc_fence_before();
       mbar_arrive(&sm.sp_free);
+      const bool row_live = lse2 != -INFINITY;
       uint32_t p_packed[16], ds_packed[16];
 #pragma unroll
       for (int i = 0; i < 32; i += 2) {
         float pr[2], ds[2];
 #pragma unroll
         for (int e = 0; e < 2; ++e) {
-          const bool live = key_live && lse2[i + e] != -INFINITY;
-          pr[e] = live ? fast_exp2(fmaf(__uint_as_float(s_bits[i + e]), sl2, -lse2[i + e])) : 0.f;
-          ds[e] = pr[e] * (__uint_as_float(dp_bits[i + e]) - delta[i + e]) * p.scale;
+          const bool live = row_live && (half * 32 + i + e < kv_size);
+          pr[e] = live ? fast_exp2(fmaf(__uint_as_float(s_bits[i + e]), sl2, -lse2)) : 0.f;
+          ds[e] = pr[e] * (__uint_as_float(dp_bits[i + e]) - delta) * p.scale;
         }
         p_packed[i >> 1] = pack_bf16(pr[0], pr[1]);
         ds_packed[i >> 1] = pack_bf16(ds[0], ds[1]);
