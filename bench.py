@@ -353,8 +353,12 @@ def main():
         kernels = kernel_rooflines(layout, leaves, dy, scale, flops, peaks)
         name = max(kernels, key=lambda n: kernels[n]["ms"])
         top = kernels[name]
-        traffic = json.loads((ROOT / "profiles" / "traffic.json").read_text()).get(name) \
-            if (ROOT / "profiles" / "traffic.json").exists() else None
+        # DRAM bytes per listed block pair from the ncu captures of the 6-head single sample
+        # (profiles/<kernel>_720p_single_sample_h6.md: dram read + write over 2,623,488 pairs),
+        # scaled to this workload by its number of listed pairs (traffic grows with the tiles).
+        per_pair = {"fine_fwd_kernel": 1283.7, "fine_bwd_dq_kernel": 1072.5, "fine_bwd_dkv_kernel": 2401.2}
+        listed = float(layout.routing_counts.sum().item())
+        traffic = per_pair[name] * listed
         result["roofline"] = {"kernel": name, "bound": "tensor", "achieved": top["achieved"],
                               "peak": peaks["tflops"], "unit": "TFLOP/s", "frac": top["frac"],
                               "traffic": traffic, "peak_source": f"{peaks['source']} burst BF16",
