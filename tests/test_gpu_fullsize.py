@@ -73,10 +73,11 @@ def test_packed_sample_gate_term_backward_linearity_and_fine_only_samples():
     ratio = (with_gate[vsa_rows].float() - base[vsa_rows].float()) / gate[vsa_rows].float()
     block_of_row = (layout.row_slot[vsa_rows] // BLOCK).long()
     strong = gate[vsa_rows].float().abs() > 1.0
-    sums = torch.zeros((layout.blocks, heads, 128), device="cuda").index_add_(0, block_of_row, ratio * strong)
+    ratio = torch.where(strong, ratio, torch.zeros_like(ratio))
+    sums = torch.zeros((layout.blocks, heads, 128), device="cuda").index_add_(0, block_of_row, ratio)
     cnt = torch.zeros((layout.blocks, heads, 128), device="cuda").index_add_(0, block_of_row, strong.float())
     mean = sums / cnt.clamp_min(1)
-    spread = ((ratio - mean[block_of_row]) * strong).abs().max().item()
+    spread = torch.where(strong, ratio - mean[block_of_row], torch.zeros_like(ratio)).abs().max().item()
     assert spread < 6e-2, spread  # BF16 rounding of out and out(0) divided by |gate| > 1
     # The backward pass is linear in dO.
     leaves = [x.clone().requires_grad_() for x in (q, k, v, gate)]
