@@ -31,14 +31,14 @@ EncodeTiled encode_tiled() {
 // (64 elements, rows, heads, 2 halves of the head dim) so that ONE box of 64 x 64 x 1 x 2 brings a
 // whole 64-row tile into shared memory as [half][row][128 bytes] with the 128-byte swizzle that
 // tcgen05 shared-memory descriptors expect.
-int make_tile_map(CUtensorMap* map, const void* base, int64_t rows, int32_t heads) {
+int make_tile_map(CUtensorMap* map, const void* base, int64_t rows, int32_t heads, int halves_per_box = 2) {
   EncodeTiled encode = encode_tiled();
   if (encode == nullptr) return vsa::kNoDriverEntry;
   if ((reinterpret_cast<uintptr_t>(base) & 15) != 0) return vsa::kBadArgument;
   const cuuint64_t row_bytes = static_cast<cuuint64_t>(heads) * vsa::kDim * 2;
   const cuuint64_t dims[4] = {64, static_cast<cuuint64_t>(rows), static_cast<cuuint64_t>(heads), 2};
   const cuuint64_t strides[3] = {row_bytes, vsa::kDim * 2, 128};
-  const cuuint32_t box[4] = {64, vsa::kBlock, 1, 2};
+  const cuuint32_t box[4] = {64, vsa::kBlock, 1, static_cast<cuuint32_t>(halves_per_box)};
   const cuuint32_t elem[4] = {1, 1, 1, 1};
   const CUresult res = encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), dims, strides, box,
                               elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
@@ -137,6 +137,7 @@ int vsa_fine_fwd(const void* q, const void* k, const void* v, int64_t q_blocks, 
   vsa::FineFwdParams p{};
   int rc = make_tile_map(&p.q_map, q, q_blocks * vsa::kBlock, heads);
   if (rc == vsa::kOk) rc = make_tile_map(&p.k_map, k, kv_blocks * vsa::kBlock, heads);
+  if (rc == vsa::kOk) rc = make_tile_map(&p.k_half_map, k, kv_blocks * vsa::kBlock, heads, 1);
   if (rc == vsa::kOk) rc = make_tile_map(&p.v_map, v, kv_blocks * vsa::kBlock, heads);
   if (rc != vsa::kOk) return rc;
   p.indices = indices;

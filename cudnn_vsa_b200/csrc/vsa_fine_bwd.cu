@@ -32,14 +32,18 @@ VSA_DEVICE float fast_exp2(float x) {
   return y;
 }
 
+// The issue helpers build each operand's descriptor low word once per product and advance it
+// with immediates: the issuing thread is alone in its warp, and per-MMA descriptor arithmetic
+// would cost more cycles than the MMA runs for.
+//
 // D[64 x 64] = A[64 x 128] B[64 x 128]^T, both K-major tiles made of two 64-wide halves.
 VSA_DEVICE void issue_nt_128(uint32_t tmem_d, const uint8_t* a, const uint8_t* b) {
   constexpr uint32_t idesc = umma_idesc(64, 64, 0, 0);
+  const uint32_t a_lo = umma_desc_lo(smem_u32(a), 16), b_lo = umma_desc_lo(smem_u32(b), 16);
 #pragma unroll
   for (int ks = 0; ks < 8; ++ks) {
-    const uint32_t off = (ks >> 2) * kHalfTileBytes + (ks & 3) * 32;
-    umma_ss(tmem_d, umma_smem_desc(smem_u32(a) + off, 16, 1024), umma_smem_desc(smem_u32(b) + off, 16, 1024),
-            idesc, ks > 0);
+    const uint32_t off = ((ks >> 2) * kHalfTileBytes + (ks & 3) * 32) >> 4;
+    umma_ss_lo(tmem_d, a_lo + off, b_lo + off, idesc, ks > 0);
   }
 }
 
@@ -48,11 +52,10 @@ VSA_DEVICE void issue_nt_128(uint32_t tmem_d, const uint8_t* a, const uint8_t* b
 // the "x 128-wide output" products (dQ^T = K^T dS^T, dV^T = dO^T P, dK^T = Q^T dS).
 VSA_DEVICE void issue_tn_128(uint32_t tmem_d, const uint8_t* a, const uint8_t* b, bool accumulate) {
   constexpr uint32_t idesc = umma_idesc(128, 64, 1, 0);
+  const uint32_t a_lo = umma_desc_lo(smem_u32(a), kHalfTileBytes), b_lo = umma_desc_lo(smem_u32(b), 16);
 #pragma unroll
-  for (int ks = 0; ks < 4; ++ks) {
-    umma_ss(tmem_d, umma_smem_desc(smem_u32(a) + ks * 2048, kHalfTileBytes, 1024),
-            umma_smem_desc(smem_u32(b) + ks * 32, 16, 1024), idesc, accumulate || ks > 0);
-  }
+  for (int ks = 0; ks < 4; ++ks)
+    umma_ss_lo(tmem_d, a_lo + ks * (2048 >> 4), b_lo + ks * (32 >> 4), idesc, accumulate || ks > 0);
 }
 
 // D^T[128 x 64] (+)= A^T B with A a row-major [64 rows][128 dims] tile read MN-major and B a
@@ -60,11 +63,10 @@ VSA_DEVICE void issue_tn_128(uint32_t tmem_d, const uint8_t* a, const uint8_t* b
 // dV^T = dO^T P and dK^T = Q^T dS with P, dS stored [query][key].
 VSA_DEVICE void issue_tt_128(uint32_t tmem_d, const uint8_t* a, const uint8_t* b, bool accumulate) {
   constexpr uint32_t idesc = umma_idesc(128, 64, 1, 1);
+  const uint32_t a_lo = umma_desc_lo(smem_u32(a), kHalfTileBytes), b_lo = umma_desc_lo(smem_u32(b), kHalfTileBytes);
 #pragma unroll
-  for (int ks = 0; ks < 4; ++ks) {
-    umma_ss(tmem_d, umma_smem_desc(smem_u32(a) + ks * 2048, kHalfTileBytes, 1024),
-            umma_smem_desc(smem_u32(b) + ks * 2048, kHalfTileBytes, 1024), idesc, accumulate || ks > 0);
-  }
+  for (int ks = 0; ks < 4; ++ks)
+    umma_ss_lo(tmem_d, a_lo + ks * (2048 >> 4), b_lo + ks * (2048 >> 4), idesc, accumulate || ks > 0);
 }
 
 // Pooled-mean gradient of `block` at column `col`, already divided by the block size.

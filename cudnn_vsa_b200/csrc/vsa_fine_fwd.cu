@@ -1,22 +1,32 @@
 // Block-sparse fine attention, forward, for sm_100a.
 //
-// One CTA owns one (query block, head): 64 query rows against the listed 64-slot KV blocks.
-// K and V tiles arrive by TMA (128-byte swizzle).  Two tcgen05 products per tile:
-//   S   = Q K^T          M = 64 query rows,  N = 64 keys,    K = 128   (accumulator: 64 columns)
-//   O^T += V^T P^T       M = 128 head dims,  N = 64 queries, K = 64    (accumulator: 64 columns)
-// The output is kept transposed so that its product runs with M = 128, the shape at which the
-// tensor core works at full rate (M = 64 uses half of its lanes).  V is read as an MN-major A
-// operand and P, written row-major [query][key] by the softmax threads, is the K-major B
-// operand, so nothing is transposed in shared memory.  The softmax runs on all 128 threads (two
-// threads per query row, 32 score columns each); the running maximum is raised only when it grew
-// by more than 2^8, and only then is O^T rescaled in tensor memory.  Two more warps run ahead of
-// the softmax: one issues the TMA loads, one the MMAs.  S is double-buffered in tensor memory and
-// K, V and P have two shared-memory stages each, so S_{j+1} is ready before the softmax of tile j
-// ends, the softmax of tile j+1 does not wait for the P V product of tile j, and the next tiles
-// are fetched under the current one.  Two CTAs share an SM.  The epilogue writes the normalised fine output in slot order, the natural-log
-// LSE and - when a row map is given - the merged result `fine + gate * coarse[block]` straight
-// into the caller's row order, which replaces the reference's separate restore and gate-add
-// passes (reference vsa_core.py:15-20, vsa_kernels.py:191-201, vsa.py:111-117).
+// One CTA owns one (query block, head): 64 query rows against the listed 64-slot KV blocks, taken
+// two blocks ("a pair") at a time.  K and V tiles arrive by TMA (128-byte swizzle).  Two tcgen05
+// products per pair, both with the 64 query rows as M:
+//   S  = Q K^T      N = 128 keys (two KV blocks),  K = 128 head dims   128 accumulator columns
+//   O += P V        N = 128 head dims,             K = 128 keys        128 accumulator columns
+// The probabilities never touch shared memory: the softmax threads read S from tensor memory,
+// write P back as packed BF16 over the first 64 columns of S, and the second product takes P as
+// its A operand straight from tensor memory.  The two K tiles of a pair are laid out as one
+// 128-row K-major operand ([dim half][tile][row][128 B], four 8 KiB TMA boxes); V tiles stay
+// separate and are read MN-major.
+//
+// The list is split between two softmax warpgroups: even pairs belong to warpgroup 0, odd pairs
+// to warpgroup 1, each with its own S / P buffer, its own O accumulator and its own running
+// maximum and sum (tensor memory: S0 S1 O0 O1, 4 x 128 columns, one CTA per SM).  A single thread
+// issues every MMA in the fixed order  ... P V(i)  Q K(i+2)  P V(i+1)  Q K(i+3) ...  so while one
+// warpgroup exponentiates pair i+1 the tensor core runs the products of its neighbours: the
+// exponentials (MUFU, 16 per clock per SM) and the MMAs overlap by construction instead of by
+// chance.  (Two independent CTAs per SM fall into lock-step: the tensor pipe serves their MMAs
+// alternately, both reach their softmax together and the two units take turns idling.)
+// Within a warpgroup two threads share a query row (one KV block of the pair each); the running
+// maximum is raised only when it grew by more than 2^8, and only then do the two threads of a row
+// rescale that row of their O in tensor memory - no CTA-wide synchronisation in the loop.
+// The epilogue combines the two partial results, writes the normalised fine output in slot
+// order, the natural-log LSE and - when a row map is given - the merged result
+// `fine + gate * coarse[block]` straight into the caller's row order, which replaces the
+// reference's separate restore and gate-add passes (reference vsa_core.py:15-20,
+// vsa_kernels.py:191-201, vsa.py:111-117).
 #include "vsa_common.cuh"
 #include "vsa_kernels.h"
 
@@ -24,22 +34,22 @@ namespace vsa {
 
 namespace {
 
-constexpr int kSoftmaxThreads = 128;  // warps 0..3: softmax and epilogue
-constexpr int kThreads = 192;         // warp 4: tcgen05.mma issue, warp 5: TMA loads
-constexpr int kTmemCols = 256;        // S0 [0,64)  S1 [64,128)  O^T [128,192)
-constexpr uint32_t kColO = 128;
+constexpr int kGroupThreads = 128;    // one softmax warpgroup
+constexpr int kSoftmaxThreads = 256;  // warps 0..3: warpgroup 0 (even pairs), warps 4..7: warpgroup 1 (odd pairs)
+constexpr int kThreads = 320;         // warp 8: tcgen05.mma issue, warp 9: TMA loads
+constexpr int kTmemCols = 512;        // S0 / P0 [0,128)  S1 / P1 [128,256)  O0 [256,384)  O1 [384,512)
+constexpr uint32_t kColO = 256;
+constexpr int kStages = 3;            // pair stages of K and of V (32 KiB each)
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kRescaleThreshold = 8.0f;  // log2 units
 
 struct FwdSmem {  // placed at a 1024-byte aligned address; every tile offset is a multiple of 1024
   uint8_t q[kTileBytes];
-  uint8_t k[2][kTileBytes];
-  uint8_t v[2][kTileBytes];
-  uint8_t p[2][kHalfTileBytes];
-  float alpha[2][kBlock];   // per tile of the pair and query row: factor applied when the maximum is raised
-  float inv_l[kBlock];      // per query row: 1 / softmax denominator (epilogue)
-  long long out_row[kBlock];
-  uint64_t q_full, k_full[2], v_full[2], s_done, o_done, s_free, p_ready;
+  uint8_t k[kStages][2 * kTileBytes];  // [dim half][tile of the pair][row][128 B]
+  uint8_t v[kStages][2][kTileBytes];   // [tile of the pair][dim half][row][128 B]
+  float m_part[2][kBlock], l_part[2][kBlock];  // per warpgroup and query row (epilogue)
+  uint64_t q_full, k_full[kStages], v_full[kStages], k_free[kStages], v_free[kStages];
+  uint64_t s_done[2], p_ready[2], o_final;
   uint32_t tmem_base;
   int abort_flag;
 };
@@ -50,61 +60,64 @@ VSA_DEVICE float fast_exp2(float x) {
   return y;
 }
 
-// S = Q K^T: eight K=16 steps over the two 64-wide halves of the head dimension.
-VSA_DEVICE void issue_qk(uint32_t tmem_s, const uint8_t* q, const uint8_t* k) {
-  constexpr uint32_t idesc = umma_idesc(64, 64, 0, 0);
+// S = Q K^T over one or two KV blocks: eight K=16 steps over the two 64-wide dim halves.
+// q_lo / k_lo: descriptor low words of the Q tile and of the K pair stage.
+VSA_DEVICE void issue_qk(uint32_t tmem_s, uint32_t q_lo, uint32_t k_lo, bool two) {
+  const uint32_t idesc = two ? umma_idesc(64, 128, 0, 0) : umma_idesc(64, 64, 0, 0);
 #pragma unroll
   for (int ks = 0; ks < 8; ++ks) {
-    const uint32_t off = (ks >> 2) * kHalfTileBytes + (ks & 3) * 32;
-    umma_ss(tmem_s, umma_smem_desc(smem_u32(q) + off, 16, 1024), umma_smem_desc(smem_u32(k) + off, 16, 1024),
-            idesc, ks > 0);
+    constexpr uint32_t kStep = 32 >> 4;
+    umma_ss_lo(tmem_s, q_lo + (ks >> 2) * (kHalfTileBytes >> 4) + (ks & 3) * kStep,
+               k_lo + (ks >> 2) * (kTileBytes >> 4) + (ks & 3) * kStep, idesc, ks > 0);
   }
 }
 
-// O^T (+)= V^T P^T.  A = V tile [key][dim] read MN-major (two 64-wide dim halves 8 KiB apart,
-// 16 keys = 2 KiB per K step); B = P [query][key], K-major (32 bytes per K step).
-VSA_DEVICE void issue_pv(uint32_t tmem_o, const uint8_t* p, const uint8_t* v, bool accumulate) {
-  constexpr uint32_t idesc = umma_idesc(128, 64, 1, 0);
+// O (+)= P V.  A = P in tensor memory (8 columns per 16 keys); B = V tile [key][dim] read
+// MN-major (two 64-wide dim halves 8 KiB apart, 16 keys = 2 KiB per K step).
+VSA_DEVICE void issue_pv(uint32_t tmem_o, uint32_t tmem_p, uint32_t v_lo, bool two, bool accumulate) {
+  constexpr uint32_t idesc = umma_idesc(64, 128, 0, 1);
 #pragma unroll
-  for (int ks = 0; ks < 4; ++ks) {
-    umma_ss(tmem_o, umma_smem_desc(smem_u32(v) + ks * 2048, kHalfTileBytes, 1024),
-            umma_smem_desc(smem_u32(p) + ks * 32, 16, 1024), idesc, accumulate || ks > 0);
+  for (int ks = 0; ks < 4; ++ks) umma_ts_lo(tmem_o, tmem_p + ks * 8, v_lo + ks * (2048 >> 4), idesc, accumulate || ks > 0);
+  if (two) {
+#pragma unroll
+    for (int ks = 0; ks < 4; ++ks)
+      umma_ts_lo(tmem_o, tmem_p + (4 + ks) * 8, v_lo + (kTileBytes >> 4) + ks * (2048 >> 4), idesc, 1u);
   }
 }
 
 }  // namespace
 
 template <bool kMerge>
-__global__ void __launch_bounds__(kThreads, 2) fine_fwd_kernel(const __grid_constant__ FineFwdParams p) {
+__global__ void __launch_bounds__(kThreads, 1) fine_fwd_kernel(const __grid_constant__ FineFwdParams p) {
   extern __shared__ uint8_t smem_raw[];
   FwdSmem& sm = *reinterpret_cast<FwdSmem*>(smem_raw + ((1024 - (smem_u32(smem_raw) & 1023)) & 1023));
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int qb = blockIdx.x, head = blockIdx.y;
-  const int row = warp * 16 + (lane & 15);  // query row inside the block (softmax role)
-  const int half = lane >> 4;               // which 32 score columns
+  const int group = (warp >> 2) & 1;              // softmax warpgroup (warps 0..7 only)
+  const int row = (warp & 3) * 16 + (lane & 15);  // query row inside the block (softmax role)
+  const int half = lane >> 4;                     // which KV block of the pair
   const int n = p.counts[static_cast<long long>(head) * p.count_head_stride + qb];
   const int32_t* list = p.indices + static_cast<long long>(head) * p.index_head_stride +
                         static_cast<long long>(qb) * p.capacity;
 
   if (tid == 0) {
     mbar_init(&sm.q_full, 1);
-    for (int i = 0; i < 2; ++i) {
+    for (int i = 0; i < kStages; ++i) {
       mbar_init(&sm.k_full[i], 1);
       mbar_init(&sm.v_full[i], 1);
+      mbar_init(&sm.k_free[i], 1);
+      mbar_init(&sm.v_free[i], 1);
     }
-    mbar_init(&sm.s_done, 1);
-    mbar_init(&sm.o_done, 1);
-    mbar_init(&sm.s_free, kSoftmaxThreads);
-    mbar_init(&sm.p_ready, kSoftmaxThreads);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&sm.s_done[i], 1);
+      mbar_init(&sm.p_ready[i], kGroupThreads);
+    }
+    mbar_init(&sm.o_final, 1);
     sm.abort_flag = 0;
     fence_barrier_init();
     tma_prefetch_desc(&p.q_map);
-    tma_prefetch_desc(&p.k_map);
+    tma_prefetch_desc(&p.k_half_map);
     tma_prefetch_desc(&p.v_map);
-  }
-  if (kMerge && tid < kBlock) {
-    const long long slot = static_cast<long long>(qb) * kBlock + tid;
-    sm.out_row[tid] = p.slot_row != nullptr ? p.slot_row[slot] : slot;
   }
   if (warp == 0) {
     tmem_alloc(&sm.tmem_base, kTmemCols);
@@ -118,244 +131,220 @@ __global__ void __launch_bounds__(kThreads, 2) fine_fwd_kernel(const __grid_cons
   volatile int* abort_flag = &sm.abort_flag;
 
   const float sl2 = p.scale * kLog2e;
-  float m_ref = -INFINITY;  // running reference maximum of the raw scores
+  float m_ref = -INFINITY;  // running reference maximum of the raw scores (this warpgroup's pairs)
   float l = 0.f;            // running sum of exp2((s - m_ref) * sl2) over this thread's columns
 
-  // Tiles are processed two at a time ("pair" i = tiles 2i and 2i+1): the softmax warps pull both
-  // score tiles into registers, release the S buffers, and pay for one fence, one consensus
-  // barrier and one arrival per pair.  Barrier discipline: a barrier is only ever waited on for its
-  // NEWEST commit or arrival round (a wait for an older phase could find the barrier two phases
-  // ahead and block); every producer/consumer edge below is ordered so that this holds.
+  // Barrier discipline: a barrier is only ever waited on for its NEWEST commit or arrival round
+  // (a wait for an older phase could find the barrier two phases ahead and block).  Every
+  // barrier below belongs to one buffer, and the round that follows the awaited one on the same
+  // barrier cannot start before the waiter has moved on.
   const int pairs = (n + 1) >> 1;
-  if (warp == 5) {
+  if (warp == 9) {
     // ------------------------------------------------------------ producer: TMA loads
     if (lane == 0 && n > 0) {
       mbar_expect_tx(&sm.q_full, kTileBytes);
       tma_load_tile(sm.q, &p.q_map, &sm.q_full, head, qb);
-      auto load_k = [&](int i) {
-        for (int t = 0; t < 2 && 2 * i + t < n; ++t) {
-          mbar_expect_tx(&sm.k_full[t], kTileBytes);
-          tma_load_tile(sm.k[t], &p.k_map, &sm.k_full[t], head, list[2 * i + t]);
-        }
-      };
-      load_k(0);
-      for (int i = 0; i < pairs; ++i) {
-        // The S products of pair i finish before the P V products of pair i-1 (they are issued
-        // first), so K of pair i+1 is fetched before V of pair i: each load starts as soon as its
-        // stage is free.  Both waits are for the newest commit on their barrier (pair i+1 cannot
-        // be issued before these loads land).
-        if (i + 1 < pairs) {
-          mbar_wait(&sm.s_done, i & 1, abort_flag, p.status, 3);
-          load_k(i + 1);
-        }
-        if (i > 0) mbar_wait(&sm.o_done, (i - 1) & 1, abort_flag, p.status, 10);
-        for (int t = 0; t < 2 && 2 * i + t < n; ++t) {
-          mbar_expect_tx(&sm.v_full[t], kTileBytes);
-          tma_load_tile(sm.v[t], &p.v_map, &sm.v_full[t], head, list[2 * i + t]);
-        }
-      }
-    }
-  } else if (warp == 4) {
-    // ------------------------------------------------------------ issuer: MMAs
-    if (lane == 0 && n > 0) {
-      mbar_wait(&sm.q_full, 0, abort_flag, p.status, 1);
       for (int i = 0; i < pairs; ++i) {
         const int count = (2 * i + 1 < n) ? 2 : 1;
-        // S buffers are free once every softmax thread holds pair i-1 in registers.
-        if (i > 0) mbar_wait(&sm.s_free, (i - 1) & 1, abort_flag, p.status, 8);
-        for (int t = 0; t < count; ++t) {
-          mbar_wait(&sm.k_full[t], i & 1, abort_flag, p.status, 2);
-          tc_fence_after();
-          issue_qk(tmem + t * 64, sm.q, sm.k[t]);
-        }
-        umma_commit(&sm.s_done);
-        if (i > 0) {
-          // P of pair i-1 is written; its P V products follow the S products of pair i so that
-          // the next softmax never waits for them.
-          const int prev = (2 * i - 1 < n) ? 2 : 1;
-          mbar_wait(&sm.p_ready, (i - 1) & 1, abort_flag, p.status, 9);
-          for (int t = 0; t < prev; ++t) {
-            mbar_wait(&sm.v_full[t], (i - 1) & 1, abort_flag, p.status, 6);
-            tc_fence_after();
-            issue_pv(tmem + kColO, sm.p[t], sm.v[t], i > 1 || t > 0);
-          }
-          umma_commit(&sm.o_done);
-        }
+        const int stage = i % kStages;
+        const uint32_t reuse = ((i / kStages) - 1) & 1;  // phase of the release by pair i - kStages
+        if (i >= kStages) mbar_wait(&sm.k_free[stage], reuse, abort_flag, p.status, 3);
+        mbar_expect_tx(&sm.k_full[stage], count * kTileBytes);
+        for (int t = 0; t < count; ++t)
+          for (int h = 0; h < 2; ++h)
+            tma_load_half(sm.k[stage] + h * kTileBytes + t * kHalfTileBytes, &p.k_half_map, &sm.k_full[stage], head,
+                          list[2 * i + t], h);
+        if (i >= kStages) mbar_wait(&sm.v_free[stage], reuse, abort_flag, p.status, 10);
+        mbar_expect_tx(&sm.v_full[stage], count * kTileBytes);
+        for (int t = 0; t < count; ++t) tma_load_tile(sm.v[stage][t], &p.v_map, &sm.v_full[stage], head, list[2 * i + t]);
       }
-      const int last = pairs - 1, count = (2 * last + 1 < n) ? 2 : 1;
-      mbar_wait(&sm.p_ready, last & 1, abort_flag, p.status, 9);
-      for (int t = 0; t < count; ++t) {
-        mbar_wait(&sm.v_full[t], last & 1, abort_flag, p.status, 6);
+    }
+  } else if (warp == 8) {
+    // ------------------------------------------------------------ issuer: MMAs
+    if (lane == 0 && n > 0) {
+      // Everything the loop needs is in registers: descriptor low words, barrier addresses by
+      // stage, and stage / phase counters that advance without divisions.
+      const uint32_t q_lo = umma_desc_lo(smem_u32(sm.q), 16);
+      const uint32_t k_lo0 = umma_desc_lo(smem_u32(sm.k[0]), 16);
+      const uint32_t v_lo0 = umma_desc_lo(smem_u32(sm.v[0][0]), kHalfTileBytes);
+      constexpr uint32_t kStageLo = (2 * kTileBytes) >> 4;
+      int k_stage = 0, v_stage = 0;       // stage of the next S product / the next P V product
+      uint32_t k_phase = 0, v_phase = 0;  // parity of that stage's current fill
+      auto qk = [&](int j) {
+        mbar_wait(&sm.k_full[k_stage], k_phase, abort_flag, p.status, 2);
         tc_fence_after();
-        issue_pv(tmem + kColO, sm.p[t], sm.v[t], last > 0 || t > 0);
+        issue_qk(tmem + (j & 1) * 128, q_lo, k_lo0 + k_stage * kStageLo, 2 * j + 1 < n);
+        umma_commit(&sm.s_done[j & 1]);
+        umma_commit(&sm.k_free[k_stage]);
+        if (++k_stage == kStages) {
+          k_stage = 0;
+          k_phase ^= 1;
+        }
+      };
+      mbar_wait(&sm.q_full, 0, abort_flag, p.status, 1);
+      qk(0);
+      if (pairs > 1) qk(1);
+      for (int i = 0; i < pairs; ++i) {
+        mbar_wait(&sm.p_ready[i & 1], (i >> 1) & 1, abort_flag, p.status, 9);
+        mbar_wait(&sm.v_full[v_stage], v_phase, abort_flag, p.status, 6);
+        tc_fence_after();
+        issue_pv(tmem + kColO + (i & 1) * 128, tmem + (i & 1) * 128, v_lo0 + v_stage * kStageLo, 2 * i + 1 < n, i >= 2);
+        umma_commit(&sm.v_free[v_stage]);
+        if (++v_stage == kStages) {
+          v_stage = 0;
+          v_phase ^= 1;
+        }
+        // The next S product of this warpgroup overwrites P; MMAs of one thread run in issue
+        // order, so it starts after the P V product above has read its operand.
+        if (i + 2 < pairs) qk(i + 2);
       }
-      umma_commit(&sm.o_done);
+      umma_commit(&sm.o_final);
     }
   } else {
-    // ------------------------------------------------------------ softmax warps
+    // ------------------------------------------------------------ softmax warpgroups
+    const uint32_t tmem_s = tmem + lane_base + group * 128;
+    const uint32_t tmem_o = tmem + lane_base + kColO + group * 128;
     // The valid length of a tile comes from two dependent global loads (list, then sizes); they
-    // are issued one pair ahead so their latency never sits in the loop.
-    int size_next[2] = {kBlock, kBlock};
-    if (p.kv_sizes != nullptr) {
-      if (n > 0) size_next[0] = p.kv_sizes[list[0]];
-      if (n > 1) size_next[1] = p.kv_sizes[list[1]];
-    }
-    for (int i = 0; i < pairs; ++i) {
-      const int count = (2 * i + 1 < n) ? 2 : 1;
-      const int kv_size[2] = {size_next[0], size_next[1]};
-      if (p.kv_sizes != nullptr) {
-        if (2 * i + 2 < n) size_next[0] = p.kv_sizes[list[2 * i + 2]];
-        if (2 * i + 3 < n) size_next[1] = p.kv_sizes[list[2 * i + 3]];
-      }
-      mbar_wait(&sm.s_done, i & 1, abort_flag, p.status, 3);
+    // are issued one round ahead so their latency never sits in the loop.
+    int size_next = kBlock;
+    if (p.kv_sizes != nullptr && 2 * group + half < n) size_next = p.kv_sizes[list[2 * group + half]];
+    for (int i = group; i < pairs; i += 2) {
+      const bool present = 2 * i + half < n;  // an odd list ends with half a pair
+      const int kv_size = present ? size_next : 0;
+      if (p.kv_sizes != nullptr && 2 * i + 4 + half < n) size_next = p.kv_sizes[list[2 * i + 4 + half]];
+      // The commit also covers every earlier MMA, so this warpgroup's O is stable until p_ready.
+      mbar_wait(&sm.s_done[group], (i >> 1) & 1, abort_flag, p.status, 3);
       tc_fence_after();
-      uint32_t s_bits[2][32];
-      VSA_TMEM_LD_16x32bx2_X32(s_bits[0], tmem + lane_base, 32);
-      if (count == 2) VSA_TMEM_LD_16x32bx2_X32(s_bits[1], tmem + lane_base + 64, 32);
+      uint32_t s_bits[64];
+      VSA_TMEM_LD_16x32bx2_X32(s_bits, tmem_s, 64);
+      VSA_TMEM_LD_16x32bx2_X32((s_bits + 32), tmem_s + 32, 64);
       tmem_wait_ld();
-      tc_fence_before();
-      mbar_arrive(&sm.s_free);
-
-      bool raise_any = false;
-      uint32_t packed[2][16];
+      float s[64];
+      if (kv_size < kBlock) {
 #pragma unroll
-      for (int t = 0; t < 2; ++t) {
-        if (t < count) {
-          float s[32];
-          if (kv_size[t] < kBlock) {
+        for (int e = 0; e < 64; ++e) s[e] = e < kv_size ? __uint_as_float(s_bits[e]) : -INFINITY;
+      } else {
 #pragma unroll
-            for (int e = 0; e < 32; ++e)
-              s[e] = (half * 32 + e < kv_size[t]) ? __uint_as_float(s_bits[t][e]) : -INFINITY;
-          } else {
-#pragma unroll
-            for (int e = 0; e < 32; ++e) s[e] = __uint_as_float(s_bits[t][e]);
-          }
-          // Four independent chains keep the dependent-latency path short.
-          float m4[4] = {s[0], s[1], s[2], s[3]};
-#pragma unroll
-          for (int e = 4; e < 32; ++e) m4[e & 3] = fmaxf(m4[e & 3], s[e]);
-          float m_tile = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
-          m_tile = fmaxf(m_tile, __shfl_xor_sync(0xffffffffu, m_tile, 16));
-          const float m_new = fmaxf(m_ref, m_tile);
-          // Raise the reference maximum only when it moved by more than 2^8; both threads of a
-          // row see the same m_tile, so they decide alike.
-          const bool raise = (m_new > m_ref) && (m_ref == -INFINITY || (m_new - m_ref) * sl2 > kRescaleThreshold);
-          float alpha = 1.f;
-          if (raise) {
-            alpha = (m_ref == -INFINITY) ? 0.f : fast_exp2((m_ref - m_new) * sl2);
-            m_ref = m_new;
-          }
-          // alpha[t][row]: factor for everything accumulated before tile t of this pair.
-          if (half == 0) sm.alpha[t][row] = alpha;
-          raise_any |= raise && (i > 0 || t > 0);
-          if (t == 1 && raise) {
-            // Tile 0 of this pair was scaled with the old reference: bring its P up to date.
-#pragma unroll
-            for (int e = 0; e < 16; ++e) {
-              const float2 f = unpack_bf16(packed[0][e]);
-              packed[0][e] = pack_bf16(f.x * alpha, f.y * alpha);
-            }
-          }
-          const float m_use = (m_ref == -INFINITY) ? 0.f : m_ref * sl2;
-          float sum4[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-          for (int e = 0; e < 32; e += 2) {
-            const float p0 = fast_exp2(fmaf(s[e], sl2, -m_use));
-            const float p1 = fast_exp2(fmaf(s[e + 1], sl2, -m_use));
-            packed[t][e >> 1] = pack_bf16(p0, p1);
-            sum4[(e >> 1) & 3] += p0 + p1;
-          }
-          l = l * alpha + ((sum4[0] + sum4[1]) + (sum4[2] + sum4[3]));
-        } else if (half == 0) {
-          sm.alpha[t][row] = 1.f;
-        }
+        for (int e = 0; e < 64; ++e) s[e] = __uint_as_float(s_bits[e]);
       }
-      // P buffers were last read by the P V products of pair i-1, the newest commit on o_done.
-      if (i > 0) mbar_wait(&sm.o_done, (i - 1) & 1, abort_flag, p.status, 5);
+      // Four independent chains keep the dependent-latency path short.
+      float m4[4] = {s[0], s[1], s[2], s[3]};
 #pragma unroll
-      for (int t = 0; t < 2; ++t) {
-        if (t < count) {
-#pragma unroll
-          for (int c = 0; c < 4; ++c)
-            *reinterpret_cast<uint4*>(sm.p[t] + swizzled_offset(row, half * 4 + c)) =
-                make_uint4(packed[t][4 * c], packed[t][4 * c + 1], packed[t][4 * c + 2], packed[t][4 * c + 3]);
-        }
+      for (int e = 4; e < 64; ++e) m4[e & 3] = fmaxf(m4[e & 3], s[e]);
+      float m_pair = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
+      m_pair = fmaxf(m_pair, __shfl_xor_sync(0xffffffffu, m_pair, 16));
+      const float m_new = fmaxf(m_ref, m_pair);
+      // Raise the reference maximum only when it moved by more than 2^8; both threads of a row
+      // see the same m_pair, so they decide alike.
+      const bool raise = (m_new > m_ref) && (m_ref == -INFINITY || (m_new - m_ref) * sl2 > kRescaleThreshold);
+      float alpha = 1.f;
+      if (raise) {
+        alpha = (m_ref == -INFINITY) ? 0.f : fast_exp2((m_ref - m_new) * sl2);
+        m_ref = m_new;
       }
-      fence_proxy_async_smem();
-      if (named_barrier_or(1, kSoftmaxThreads, raise_any)) {
-        // Rare: scale column r of O^T (lane = head dim, column = query row) by the factors of
-        // both tiles.  O^T is stable here: the P V products of pair i-1 are complete.
-        tc_fence_after();
+      if (__any_sync(0xffffffffu, raise && i >= 2)) {
+        // Rare: this thread scales its 64 columns of its row of O.
 #pragma unroll
         for (int c = 0; c < 2; ++c) {
           uint32_t o_bits[32];
-          const uint32_t addr = tmem + lane_base + kColO + c * 32;
-          VSA_TMEM_LD_32x32b_X32(o_bits, addr);
+          VSA_TMEM_LD_16x32bx2_X32(o_bits, tmem_o + c * 32, 64);
           tmem_wait_ld();
 #pragma unroll
-          for (int e = 0; e < 32; ++e)
-            o_bits[e] = __float_as_uint(__uint_as_float(o_bits[e]) * (sm.alpha[0][c * 32 + e] * sm.alpha[1][c * 32 + e]));
-          VSA_TMEM_ST_32x32b_X32(o_bits, addr);
+          for (int e = 0; e < 32; ++e) o_bits[e] = __float_as_uint(__uint_as_float(o_bits[e]) * alpha);
+          VSA_TMEM_ST_16x32bx2_X32(o_bits, tmem_o + c * 32, 64);
         }
-        tmem_wait_st();
-        // alpha[] is rewritten next iteration: every reader must be done first.
-        named_barrier(1, kSoftmaxThreads);
       }
+      const float m_use = (m_ref == -INFINITY) ? 0.f : m_ref * sl2;
+      uint32_t packed[32];
+      float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int e = 0; e < 64; e += 2) {
+        const float p0 = fast_exp2(fmaf(s[e], sl2, -m_use));
+        const float p1 = fast_exp2(fmaf(s[e + 1], sl2, -m_use));
+        packed[e >> 1] = pack_bf16(p0, p1);
+        sum4[(e >> 1) & 3] += p0 + p1;
+      }
+      l = l * alpha + ((sum4[0] + sum4[1]) + (sum4[2] + sum4[3]));
+      // P over the first 64 columns of S: keys of the pair's first block in columns [0,32), of
+      // its second block in [32,64).  Every S read of this warp has completed (wait::ld above).
+      VSA_TMEM_ST_16x32bx2_X32(packed, tmem_s, 32);
+      tmem_wait_st();
       tc_fence_before();
-      mbar_arrive(&sm.p_ready);
+      mbar_arrive(&sm.p_ready[group]);
     }
   }
 
   // ---------------------------------------------------------------- epilogue
-  const long long width = static_cast<long long>(p.heads) * kDim;
-  if (warp < 4) {
-  l += __shfl_xor_sync(0xffffffffu, l, 16);
-  if (half == 0) {
-    sm.inv_l[row] = l > 0.f ? 1.f / l : 0.f;
-    const long long slot = static_cast<long long>(qb) * kBlock + row;
-    p.lse[static_cast<long long>(head) * p.q_slots + slot] = l > 0.f ? m_ref * p.scale + logf(l) : -INFINITY;
-  }
-  if (n > 0) {
-    mbar_wait(&sm.o_done, (pairs - 1) & 1, abort_flag, p.status, 7);
-    tc_fence_after();
-  }
-  named_barrier(1, kSoftmaxThreads);
-  // Thread = head dim `dim`; its 64 accumulator columns are the 64 query rows.  A warp writes 32
-  // consecutive BF16 (64 bytes) of one row per store.
-  const int dim = tid;
-  const long long col = static_cast<long long>(head) * kDim + dim;
-  float coarse = 0.f;
-  bool gated = false;
-  if (kMerge) {
-    const int coarse_slot = p.block_coarse != nullptr ? p.block_coarse[qb] : -1;
-    gated = coarse_slot >= 0;
-    if (gated) coarse = __bfloat162float(p.coarse[coarse_slot * width + col]);
-  }
-#pragma unroll
-  for (int c = 0; c < 2; ++c) {
-    uint32_t o_bits[32] = {};
-    if (n > 0) {
-      VSA_TMEM_LD_32x32b_X32(o_bits, tmem + lane_base + kColO + c * 32);
-      tmem_wait_ld();
+  if (warp < 8) {
+    const long long width = static_cast<long long>(p.heads) * kDim;
+    l += __shfl_xor_sync(0xffffffffu, l, 16);
+    if (half == 0) {
+      sm.m_part[group][row] = m_ref;
+      sm.l_part[group][row] = l;
     }
+    if (n > 0) {
+      mbar_wait(&sm.o_final, 0, abort_flag, p.status, 7);
+      tc_fence_after();
+    }
+    named_barrier(1, kSoftmaxThreads);
+    // Combine the two warpgroups' partial softmax results of this row.
+    const float m0 = sm.m_part[0][row], m1 = sm.m_part[1][row];
+    const float l0 = sm.l_part[0][row], l1 = sm.l_part[1][row];
+    const float m_all = fmaxf(m0, m1);
+    const float a0 = l0 > 0.f ? fast_exp2((m0 - m_all) * sl2) : 0.f;
+    const float a1 = l1 > 0.f ? fast_exp2((m1 - m_all) * sl2) : 0.f;
+    const float l_all = l0 * a0 + l1 * a1;
+    const float inv_l = l_all > 0.f ? 1.f / l_all : 0.f;
+    const float w0 = a0 * inv_l, w1 = a1 * inv_l;
+    const long long slot = static_cast<long long>(qb) * kBlock + row;
+    if (half == 0 && group == 0)
+      p.lse[static_cast<long long>(head) * p.q_slots + slot] = l_all > 0.f ? m_all * p.scale + logf(l_all) : -INFINITY;
+    // Thread = (query row, 32 head dims): 64 contiguous bytes of one output row.
+    const int dim0 = half * 64 + group * 32;
+    const long long col = static_cast<long long>(head) * kDim + dim0;
+    long long out_row = -1;
+    const uint4* gate = nullptr;
+    const uint4* coarse = nullptr;
+    if (kMerge) {
+      out_row = p.slot_row != nullptr ? p.slot_row[slot] : slot;
+      if (out_row >= p.out_rows) out_row = -1;
+      const int coarse_slot = p.block_coarse != nullptr ? p.block_coarse[qb] : -1;
+      if (coarse_slot >= 0 && out_row >= 0) {
+        gate = reinterpret_cast<const uint4*>(p.gate + out_row * width + col);
+        coarse = reinterpret_cast<const uint4*>(p.coarse + coarse_slot * width + col);
+      }
+    }
+    uint4* o_dst = reinterpret_cast<uint4*>(p.o_slots + slot * width + col);
+    uint4* out_dst = (kMerge && out_row >= 0) ? reinterpret_cast<uint4*>(p.out + out_row * width + col) : nullptr;
+    uint32_t o0[32] = {}, o1[32] = {};
+    // A warpgroup without pairs never wrote its accumulator: its columns are not read (the
+    // conditions are uniform over the CTA, as the warp-wide loads require).
+    if (pairs > 0) VSA_TMEM_LD_16x32bx2_X32(o0, tmem + lane_base + kColO + group * 32, 64);
+    if (pairs > 1) VSA_TMEM_LD_16x32bx2_X32(o1, tmem + lane_base + kColO + 128 + group * 32, 64);
+    tmem_wait_ld();
 #pragma unroll
-    for (int i = 0; i < 32; ++i) {
-      const int r = c * 32 + i;
-      const float o = __uint_as_float(o_bits[i]) * sm.inv_l[r];
-      const long long slot = static_cast<long long>(qb) * kBlock + r;
-      p.o_slots[slot * width + col] = __float2bfloat16(o);
-      if (kMerge) {
-        const long long out_row = sm.out_row[r];
-        if (out_row >= 0 && out_row < p.out_rows) {
-          float merged = o;
-          // Product and sum are rounded separately, as the reference's merge does.
-          if (gated) merged = __fadd_rn(o, __fmul_rn(__bfloat162float(p.gate[out_row * width + col]), coarse));
-          p.out[out_row * width + col] = __float2bfloat16(merged);
+    for (int v4 = 0; v4 < 4; ++v4) {
+      float o[8];
+#pragma unroll
+      for (int e = 0; e < 8; ++e)
+        o[e] = __uint_as_float(o0[v4 * 8 + e]) * w0 + __uint_as_float(o1[v4 * 8 + e]) * w1;
+      o_dst[v4] = make_uint4(pack_bf16(o[0], o[1]), pack_bf16(o[2], o[3]), pack_bf16(o[4], o[5]), pack_bf16(o[6], o[7]));
+      if (kMerge && out_dst != nullptr) {
+        if (gate != nullptr) {
+          const uint4 g = gate[v4], cz = coarse[v4];
+          const uint32_t gw[4] = {g.x, g.y, g.z, g.w}, cw[4] = {cz.x, cz.y, cz.z, cz.w};
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const float2 gf = unpack_bf16(gw[e]), cf = unpack_bf16(cw[e]);
+            // Product and sum are rounded separately, as the reference's merge does.
+            o[2 * e] = __fadd_rn(o[2 * e], __fmul_rn(gf.x, cf.x));
+            o[2 * e + 1] = __fadd_rn(o[2 * e + 1], __fmul_rn(gf.y, cf.y));
+          }
         }
+        out_dst[v4] = make_uint4(pack_bf16(o[0], o[1]), pack_bf16(o[2], o[3]), pack_bf16(o[4], o[5]), pack_bf16(o[6], o[7]));
       }
     }
   }
-  }  // softmax warps
   tc_fence_before();
   __syncthreads();
   if (warp == 0) tmem_dealloc(tmem, kTmemCols);

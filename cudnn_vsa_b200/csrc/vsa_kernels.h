@@ -10,6 +10,7 @@ namespace vsa {
 // ---------------------------------------------------------------------------- fine attention
 struct FineFwdParams {
   CUtensorMap q_map, k_map, v_map;  // [slots, heads, 128] BF16, box 64 x 1 x 64, 128-byte swizzle
+  CUtensorMap k_half_map;           // same tensor as k_map, box = one 64-element half of a tile
   const int32_t* indices;           // [heads?, q_blocks, capacity] listed KV blocks, ascending
   const int32_t* counts;            // [heads?, q_blocks]
   long long index_head_stride;      // elements between heads (0 = one table for all heads)
