@@ -211,6 +211,10 @@ int vsa_fine_bwd(const void* q, const void* k, const void* v, const void* d_o, i
   if (rc == vsa::kOk) rc = make_tile_map(&p.k_map, k, kv_blocks * vsa::kBlock, heads);
   if (rc == vsa::kOk) rc = make_tile_map(&p.v_map, v, kv_blocks * vsa::kBlock, heads);
   if (rc == vsa::kOk) rc = make_tile_map(&p.do_map, d_o, q_blocks * vsa::kBlock, heads);
+  if (rc == vsa::kOk) rc = make_tile_map(&p.k_half_map, k, kv_blocks * vsa::kBlock, heads, 1);
+  if (rc == vsa::kOk) rc = make_tile_map(&p.v_half_map, v, kv_blocks * vsa::kBlock, heads, 1);
+  if (rc == vsa::kOk) rc = make_tile_map(&p.q_half_map, q, q_blocks * vsa::kBlock, heads, 1);
+  if (rc == vsa::kOk) rc = make_tile_map(&p.do_half_map, d_o, q_blocks * vsa::kBlock, heads, 1);
   if (rc != vsa::kOk) return rc;
   p.indices = indices;
   p.counts = counts;

@@ -1,0 +1,306 @@
+// Block-sparse fine attention, backward, dQ kernel for sm_100a.
+//
+// One CTA owns one (query block, head) and walks the block's KV list two blocks ("a pair") at a
+// time.  Every product puts 128 rows on the tensor core's M axis, the shape it runs at full rate:
+//   S^T  = K Q^T        M = 128 keys of the pair,  N = 64 queries,  K = 128 head dims
+//   dP^T = V dO^T       M = 128 keys,              N = 64 queries,  K = 128 head dims
+//   dQ^T += K^T dS^T    M = 128 head dims,         N = 64 queries,  K = 128 keys
+// With the keys on the TMEM lanes a thread of a score-math warpgroup owns one key and sees the
+// 64 queries along its columns; the per-query LSE and delta are the same for every pair, so they
+// sit in shared memory (pre-scaled) and are read as broadcasts.  P is recomputed from the saved
+// LSE (natural log), dS^T = P^T * (dP^T - delta) * scale is written as BF16 rows [key][query],
+// which is directly the MN-major B operand of the third product; K^T is the K pair read MN-major.
+// Two warpgroups take alternate pairs, each with its own S^T / dP^T accumulators and dS^T buffer,
+// and one thread issues every MMA in the fixed order  ... dQ(i)  S,dP(i+2)  dQ(i+1)  S,dP(i+3) ...
+// so the exponentials of one pair run under the products of its neighbours.  K pair stages are
+// held until their dQ product has read them (three stages), V pair stages only until dP^T (two).
+// The epilogue adds the gradient that reaches a row through its block's pooled mean and scatters
+// the rows to the caller's row order, skipping padding slots (reference vsa_core.py:23-30, 42-47;
+// vsa_kernels.py:86-96, 161-176 adjoint).
+#include "vsa_common.cuh"
+#include "vsa_kernels.h"
+#include "vsa_bwd_common.cuh"
+
+namespace vsa {
+
+namespace {
+
+constexpr int kGroupThreads = 128;  // one score-math warpgroup
+constexpr int kMathThreads = 256;   // warps 0..3: warpgroup 0 (even pairs), warps 4..7: warpgroup 1 (odd pairs)
+constexpr int kThreads = 320;       // warp 8: tcgen05.mma issue, warp 9: TMA loads
+constexpr int kTmemCols = 512;      // per warpgroup g: S^T [128g, 128g+64)  dP^T [128g+64, 128g+128);  dQ^T [256,320)
+constexpr uint32_t kColDq = 256;
+constexpr int kKStages = 3;
+constexpr int kVStages = 2;
+constexpr int kPairBytes = 2 * kTileBytes;  // [dim half][tile of the pair][row][128 B]
+
+struct DqSmem {  // placed at a 1024-byte aligned address; every tile offset is a multiple of 1024
+  uint8_t q[kTileBytes];
+  uint8_t d_o[kTileBytes];
+  uint8_t k[kKStages][kPairBytes];
+  uint8_t v[kVStages][kPairBytes];
+  uint8_t ds[2][kTileBytes];  // per warpgroup: dS^T [128 keys][64 queries] BF16, 128-byte swizzle
+  float neg_lse2[kBlock];     // -lse * log2(e) per query row (-inf for a row without keys)
+  float delta[kBlock];
+  long long out_row[kBlock];
+  uint64_t qdo_full, k_full[kKStages], v_full[kVStages], k_free[kKStages], v_free[kVStages];
+  uint64_t sp_done[2], ds_ready[2], ds_free[2], dq_final;
+  uint32_t tmem_base;
+  int abort_flag;
+};
+
+// S^T or dP^T = A B^T: A = a K-major pair stage (128 rows), B = a K-major 64-row tile; eight
+// K=16 steps over the two 64-wide dim halves.
+VSA_DEVICE void issue_scores(uint32_t tmem_d, uint32_t pair_lo, uint32_t tile_lo) {
+  constexpr uint32_t idesc = umma_idesc(128, 64, 0, 0);
+#pragma unroll
+  for (int ks = 0; ks < 8; ++ks)
+    umma_ss_lo(tmem_d, pair_lo + (ks >> 2) * (kTileBytes >> 4) + (ks & 3) * 2,
+               tile_lo + (ks >> 2) * (kHalfTileBytes >> 4) + (ks & 3) * 2, idesc, ks > 0);
+}
+
+// dQ^T (+)= K^T dS^T over the keys of one or two blocks: A = the K pair read MN-major (16 keys =
+// 2 KiB per step, dim halves 16 KiB apart), B = dS^T rows [key][query] read MN-major.
+VSA_DEVICE void issue_dq(uint32_t tmem_d, uint32_t k_mn_lo, uint32_t ds_lo, bool two, bool accumulate) {
+  constexpr uint32_t idesc = umma_idesc(128, 64, 1, 1);
+#pragma unroll
+  for (int ks = 0; ks < 4; ++ks) umma_ss_lo(tmem_d, k_mn_lo + ks * 128, ds_lo + ks * 128, idesc, accumulate || ks > 0);
+  if (two) {
+#pragma unroll
+    for (int ks = 4; ks < 8; ++ks) umma_ss_lo(tmem_d, k_mn_lo + ks * 128, ds_lo + ks * 128, idesc, 1u);
+  }
+}
+
+}  // namespace
+
+__global__ void __launch_bounds__(kThreads, 1) fine_bwd_dq_kernel(const __grid_constant__ FineBwdParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  DqSmem& sm = *reinterpret_cast<DqSmem*>(smem_raw + ((1024 - (smem_u32(smem_raw) & 1023)) & 1023));
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int qb = blockIdx.x, head = blockIdx.y;
+  const int group = (warp >> 2) & 1;  // score-math warpgroup (warps 0..7 only)
+  const int key = tid & 127;          // key of the pair owned by this thread (math role) / head dim (epilogue)
+  const int n = p.counts[static_cast<long long>(head) * p.count_head_stride + qb];
+  const int32_t* list = p.indices + static_cast<long long>(head) * p.index_head_stride +
+                        static_cast<long long>(qb) * p.capacity;
+
+  if (tid == 0) {
+    mbar_init(&sm.qdo_full, 1);
+    for (int i = 0; i < kKStages; ++i) {
+      mbar_init(&sm.k_full[i], 1);
+      mbar_init(&sm.k_free[i], 1);
+    }
+    for (int i = 0; i < kVStages; ++i) {
+      mbar_init(&sm.v_full[i], 1);
+      mbar_init(&sm.v_free[i], 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&sm.sp_done[i], 1);
+      mbar_init(&sm.ds_ready[i], kGroupThreads);
+      mbar_init(&sm.ds_free[i], 1);
+    }
+    mbar_init(&sm.dq_final, 1);
+    sm.abort_flag = 0;
+    fence_barrier_init();
+    tma_prefetch_desc(&p.q_map);
+    tma_prefetch_desc(&p.do_map);
+    tma_prefetch_desc(&p.k_half_map);
+    tma_prefetch_desc(&p.v_half_map);
+  }
+  if (tid < kBlock) {
+    const long long s = static_cast<long long>(qb) * kBlock + tid;
+    sm.out_row[tid] = p.q_slot_row != nullptr ? p.q_slot_row[s] : s;
+    const float lse = p.lse[static_cast<long long>(head) * p.q_slots + s];
+    sm.neg_lse2[tid] = lse == -INFINITY ? -INFINITY : -lse * kLog2eBwd;
+    sm.delta[tid] = p.delta[static_cast<long long>(head) * p.q_slots + s];
+  }
+  if (warp == 0) {
+    tmem_alloc(&sm.tmem_base, kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = sm.tmem_base;
+  const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
+  volatile int* abort_flag = &sm.abort_flag;
+
+  // Barrier discipline: a barrier is only ever waited on for its NEWEST commit or arrival round;
+  // every barrier belongs to one buffer and the round after the awaited one cannot start before
+  // the waiter has moved on.
+  const int pairs = (n + 1) >> 1;
+  if (warp == 9) {
+    // ------------------------------------------------------------ producer: TMA loads
+    if (lane == 0 && n > 0) {
+      mbar_expect_tx(&sm.qdo_full, 2 * kTileBytes);
+      tma_load_tile(sm.q, &p.q_map, &sm.qdo_full, head, qb);
+      tma_load_tile(sm.d_o, &p.do_map, &sm.qdo_full, head, qb);
+      int ks = 0, vs = 0;
+      uint32_t k_round = 0, v_round = 0;  // parity of the release awaited before refilling the stage
+      for (int i = 0; i < pairs; ++i) {
+        const int count = (2 * i + 1 < n) ? 2 : 1;
+        // V stages are released first (after dP^T), K stages after the dQ product.
+        if (i >= kVStages) mbar_wait(&sm.v_free[vs], v_round, abort_flag, p.status, 12);
+        mbar_expect_tx(&sm.v_full[vs], count * kTileBytes);
+        for (int t = 0; t < count; ++t)
+          for (int h = 0; h < 2; ++h)
+            tma_load_half(sm.v[vs] + h * kTileBytes + t * kHalfTileBytes, &p.v_half_map, &sm.v_full[vs], head,
+                          list[2 * i + t], h);
+        if (i >= kKStages) mbar_wait(&sm.k_free[ks], k_round, abort_flag, p.status, 11);
+        mbar_expect_tx(&sm.k_full[ks], count * kTileBytes);
+        for (int t = 0; t < count; ++t)
+          for (int h = 0; h < 2; ++h)
+            tma_load_half(sm.k[ks] + h * kTileBytes + t * kHalfTileBytes, &p.k_half_map, &sm.k_full[ks], head,
+                          list[2 * i + t], h);
+        if (++vs == kVStages) {
+          vs = 0;
+          if (i >= kVStages) v_round ^= 1;
+        }
+        if (++ks == kKStages) {
+          ks = 0;
+          if (i >= kKStages) k_round ^= 1;
+        }
+      }
+    }
+  } else if (warp == 8) {
+    // ------------------------------------------------------------ issuer: MMAs
+    if (lane == 0 && n > 0) {
+      const uint32_t q_lo = umma_desc_lo(smem_u32(sm.q), 16);
+      const uint32_t do_lo = umma_desc_lo(smem_u32(sm.d_o), 16);
+      const uint32_t k_lo0 = umma_desc_lo(smem_u32(sm.k[0]), 16);
+      const uint32_t k_mn_lo0 = umma_desc_lo(smem_u32(sm.k[0]), kTileBytes);
+      const uint32_t v_lo0 = umma_desc_lo(smem_u32(sm.v[0]), 16);
+      const uint32_t ds_lo0 = umma_desc_lo(smem_u32(sm.ds[0]), kHalfTileBytes);
+      constexpr uint32_t kPairLo = kPairBytes >> 4, kDsLo = kTileBytes >> 4;
+      int s_k = 0, s_v = 0, d_k = 0;              // stages of the next score products / the next dQ product
+      uint32_t s_k_phase = 0, s_v_phase = 0;      // parities of those stages' current fills
+      auto scores = [&](int j) {
+        mbar_wait(&sm.k_full[s_k], s_k_phase, abort_flag, p.status, 15);
+        mbar_wait(&sm.v_full[s_v], s_v_phase, abort_flag, p.status, 15);
+        tc_fence_after();
+        issue_scores(tmem + (j & 1) * 128, k_lo0 + s_k * kPairLo, q_lo);
+        issue_scores(tmem + (j & 1) * 128 + 64, v_lo0 + s_v * kPairLo, do_lo);
+        umma_commit(&sm.sp_done[j & 1]);
+        umma_commit(&sm.v_free[s_v]);
+        if (++s_k == kKStages) {
+          s_k = 0;
+          s_k_phase ^= 1;
+        }
+        if (++s_v == kVStages) {
+          s_v = 0;
+          s_v_phase ^= 1;
+        }
+      };
+      mbar_wait(&sm.qdo_full, 0, abort_flag, p.status, 11);
+      scores(0);
+      if (pairs > 1) scores(1);
+      for (int i = 0; i < pairs; ++i) {
+        // dS^T of pair i is in shared memory, so its warpgroup has also finished reading its
+        // S^T / dP^T accumulators: they may be overwritten by pair i + 2 below.
+        mbar_wait(&sm.ds_ready[i & 1], (i >> 1) & 1, abort_flag, p.status, 18);
+        tc_fence_after();
+        issue_dq(tmem + kColDq, k_mn_lo0 + d_k * kPairLo, ds_lo0 + (i & 1) * kDsLo, 2 * i + 1 < n, i > 0);
+        umma_commit(&sm.k_free[d_k]);
+        umma_commit(&sm.ds_free[i & 1]);
+        if (++d_k == kKStages) d_k = 0;
+        if (i + 2 < pairs) scores(i + 2);
+      }
+      umma_commit(&sm.dq_final);
+    }
+  } else {
+    // ------------------------------------------------------------ score math warpgroups
+    const uint32_t tmem_s = tmem + lane_base + group * 128;
+    uint8_t* ds_row = sm.ds[group] + key * 128;
+    const int tile = key >> 6, key_in_block = key & 63;
+    const float scale = p.scale, sl2 = p.scale * kLog2eBwd;
+    // The valid length of a block comes from two dependent global loads (list, then sizes); they
+    // are issued one round ahead so their latency never sits in the loop.
+    int size_next = kBlock;
+    if (p.kv_sizes != nullptr && 2 * group + tile < n) size_next = p.kv_sizes[list[2 * group + tile]];
+    for (int i = group; i < pairs; i += 2) {
+      const bool live = (2 * i + tile < n) && key_in_block < size_next;
+      if (p.kv_sizes != nullptr && 2 * i + 4 + tile < n) size_next = p.kv_sizes[list[2 * i + 4 + tile]];
+      mbar_wait(&sm.sp_done[group], (i >> 1) & 1, abort_flag, p.status, 13);
+      tc_fence_after();
+      uint32_t packed[32];
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        uint32_t s_bits[32], dp_bits[32];
+        VSA_TMEM_LD_32x32b_X32(s_bits, tmem_s + c * 32);
+        VSA_TMEM_LD_32x32b_X32(dp_bits, tmem_s + 64 + c * 32);
+        tmem_wait_ld();
+#pragma unroll
+        for (int e = 0; e < 32; e += 4) {
+          const float4 nl = *reinterpret_cast<const float4*>(&sm.neg_lse2[c * 32 + e]);
+          const float4 dl = *reinterpret_cast<const float4*>(&sm.delta[c * 32 + e]);
+          const float nls[4] = {nl.x, nl.y, nl.z, nl.w}, dls[4] = {dl.x, dl.y, dl.z, dl.w};
+          float ds[4];
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            // A query row without keys has neg_lse2 = -inf: exp2(-inf) = 0.
+            const float pr = fast_exp2(fmaf(__uint_as_float(s_bits[e + u]), sl2, nls[u]));
+            const float v = pr * (__uint_as_float(dp_bits[e + u]) - dls[u]) * scale;
+            ds[u] = live ? v : 0.f;  // a select: rows of an absent or padded key may hold anything
+          }
+          packed[c * 16 + (e >> 1)] = pack_bf16(ds[0], ds[1]);
+          packed[c * 16 + (e >> 1) + 1] = pack_bf16(ds[2], ds[3]);
+        }
+      }
+      // The dQ product of this warpgroup's previous pair has finished reading the dS^T buffer.
+      if (i >= 2) mbar_wait(&sm.ds_free[group], ((i >> 1) - 1) & 1, abort_flag, p.status, 14);
+#pragma unroll
+      for (int c = 0; c < 8; ++c)
+        *reinterpret_cast<uint4*>(ds_row + ((c ^ (key & 7)) << 4)) =
+            make_uint4(packed[4 * c], packed[4 * c + 1], packed[4 * c + 2], packed[4 * c + 3]);
+      fence_proxy_async_smem();
+      tc_fence_before();
+      mbar_arrive(&sm.ds_ready[group]);
+    }
+  }
+
+  // ---------------------------------------------------------------- epilogue
+  if (warp < 8) {
+    if (n > 0) {
+      mbar_wait(&sm.dq_final, 0, abort_flag, p.status, 16);
+      tc_fence_after();
+    }
+    // Thread = head dim `key`; warpgroup g takes query rows [32g, 32g+32).  A warp store covers
+    // 32 consecutive elements of one row.
+    const long long width = static_cast<long long>(p.heads) * kDim;
+    const long long col = static_cast<long long>(head) * kDim + key;
+    const int q_size = p.q_sizes != nullptr ? p.q_sizes[qb] : kBlock;
+    const float term = pool_term(p.dq_pool, p.pool_f32, p.q_block_coarse, qb, q_size, width, col);
+    uint32_t bits[32] = {};
+    if (n > 0) {
+      VSA_TMEM_LD_32x32b_X32(bits, tmem + lane_base + kColDq + group * 32);
+      tmem_wait_ld();
+    }
+#pragma unroll
+    for (int i = 0; i < 32; ++i) {
+      const int r = group * 32 + i;
+      const float value = __uint_as_float(bits[i]) + term;
+      if (p.dq_f32 != nullptr) {
+        float* dst = p.dq_f32 + (static_cast<long long>(qb) * kBlock + r) * width + col;
+        *dst = p.f32_accumulate ? *dst + value : value;
+      } else {
+        const long long row = sm.out_row[r];
+        if (row >= 0 && row < p.q_out_rows) p.dq[row * width + col] = __float2bfloat16(value);
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(tmem, kTmemCols);
+}
+
+cudaError_t launch_fine_bwd_dq(const FineBwdParams& params, cudaStream_t stream) {
+  const size_t smem = sizeof(DqSmem) + 1024;
+  cudaError_t err = cudaFuncSetAttribute(fine_bwd_dq_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         static_cast<int>(smem));
+  if (err != cudaSuccess) return err;
+  dim3 grid(params.q_blocks, params.heads);
+  fine_bwd_dq_kernel<<<grid, kThreads, smem, stream>>>(params);
+  return cudaGetLastError();
+}
+
+}  // namespace vsa

@@ -35,6 +35,8 @@ cudaError_t launch_fine_fwd(const FineFwdParams& params, bool merge, cudaStream_
 
 struct FineBwdParams {
   CUtensorMap q_map, k_map, v_map, do_map;  // all [slots, heads, 128] BF16
+  CUtensorMap k_half_map, v_half_map;       // same tensors, box = one 64-element half of a tile
+  CUtensorMap q_half_map, do_half_map;
   const int32_t* indices;
   const int32_t* counts;
   long long index_head_stride, count_head_stride;
