@@ -58,11 +58,13 @@ VSA_DEVICE bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 constexpr long long kWaitCycles = 2000000000LL;
 
 // Bounded wait.  `abort_flag` lives in shared memory; once any wait of the CTA has timed out
-// every later wait returns at once, so the CTA drains its loops, frees TMEM and exits.
+// every later wait on an incomplete barrier returns at once, so the CTA drains its loops, frees
+// TMEM and exits.  A completed barrier costs one try_wait: the waits of the MMA-issuing thread
+// sit on the critical path of the tensor pipe.
 VSA_DEVICE bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* status,
                           int site) {
-  if (*abort_flag) return false;
   if (mbar_try_wait(bar, parity)) return true;
+  if (*abort_flag) return false;
   const long long start = clock64();
   while (!mbar_try_wait(bar, parity)) {
     if (*abort_flag) return false;
@@ -250,6 +252,15 @@ VSA_DEVICE void umma_ts_lo(uint32_t tmem_d, uint32_t tmem_a, uint32_t b_lo, uint
       "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]),    \
       "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]),    \
       "r"(r[31])                                                                                        \
+      : "memory")
+
+#define VSA_TMEM_ST_16x32bx2_X16(r, taddr, split)                                                     \
+  asm volatile(                                                                                       \
+      "tcgen05.st.sync.aligned.16x32bx2.x16.b32 [%0], " #split ", "                                   \
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"                      \
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]),        \
+      "r"(r[7]), "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]),       \
+      "r"(r[15])                                                                                        \
       : "memory")
 
 // An M=128 accumulator has row r in lane r; the 32x32b shape gives lane t of the warp's quarter

@@ -56,7 +56,7 @@ VSA_DEVICE void store_grad_columns(bool have_acc, uint32_t tmem_addr, float term
 namespace {
 
 constexpr int kGroupThreads = 128;  // one score-math warpgroup
-constexpr int kDkvThreads = 320;    // warps 0..7: two score-math warpgroups, warp 8: MMA issue, warp 9: TMA loads
+constexpr int kDkvThreads = 352;    // warps 0..7: two score-math warpgroups, warp 8: MMA issue, warps 9 / 10: TMA loads of K, V, Q / of dO
 constexpr int kDkvTmemCols = 512;   // per warpgroup g: S [128g, 128g+64)  dP [128g+64, 128g+128);  dK^T [256,320)  dV^T [320,384)
 constexpr uint32_t kColDk = 256, kColDv = 320;
 constexpr int kPairBytes = 2 * kTileBytes;  // [dim half][tile of the pair][row][128 B]
@@ -69,7 +69,7 @@ struct DkvSmem {  // placed at a 1024-byte aligned address; every tile offset is
   uint8_t pt[2][kTileBytes];   // per warpgroup: P  [128 queries][64 keys] BF16, 128-byte swizzle
   uint8_t dst[2][kTileBytes];  // per warpgroup: dS [128 queries][64 keys]
   long long out_row[kBlock];
-  uint64_t kv_full, qd_full[2], qd_free[2], sp_done[2], pd_ready[2], pd_free[2], dkv_final;
+  uint64_t kv_full, q_full[2], do_full[2], q_free[2], do_free[2], sp_done[2], pd_ready[2], pd_free[2], dkv_final;
   uint32_t tmem_base;
   int abort_flag;
 };
@@ -123,9 +123,11 @@ VSA_DEVICE void issue_pair_grad(uint32_t tmem_d, uint32_t a_mn_lo, uint32_t b_lo
 // dV^T += dO^T P and dK^T += Q^T dS with the head dims on the M axis and the pair's 128 query
 // rows as K.  Query rows sit on the TMEM lanes, so a score-math thread owns one query row and
 // needs one LSE and one delta per pair.  Two warpgroups take alternate pairs, each with its own
-// S / dP accumulators and P / dS buffers; a pair's Q / dO stage is held until its gradient
-// products have read it, and with two stages the refill latency is hidden by issuing the
-// products in the order  grad(i) grad(i+1) scores(i+2) scores(i+3).
+// S / dP accumulators and P / dS buffers.  A pair's Q stage is held until its dK product has
+// read it and its dO stage until the dV product; there is room for two stages of each, so the
+// refill latency is hidden by the issue order  dK(i) dV(i) dK(i+1) dV(i+1) S(i+2) dP(i+2)
+// S(i+3) dP(i+3): every refill has about three products' time to land, and Q and dO have a
+// producer warp each so that neither load queues behind the other's wait.
 __global__ void __launch_bounds__(kDkvThreads, 1) fine_bwd_dkv_kernel(const __grid_constant__ FineBwdParams p) {
   extern __shared__ uint8_t smem_raw[];
   DkvSmem& sm = *reinterpret_cast<DkvSmem*>(smem_raw + ((1024 - (smem_u32(smem_raw) & 1023)) & 1023));
@@ -140,8 +142,10 @@ __global__ void __launch_bounds__(kDkvThreads, 1) fine_bwd_dkv_kernel(const __gr
   if (tid == 0) {
     mbar_init(&sm.kv_full, 1);
     for (int i = 0; i < 2; ++i) {
-      mbar_init(&sm.qd_full[i], 1);
-      mbar_init(&sm.qd_free[i], 1);
+      mbar_init(&sm.q_full[i], 1);
+      mbar_init(&sm.do_full[i], 1);
+      mbar_init(&sm.q_free[i], 1);
+      mbar_init(&sm.do_free[i], 1);
       mbar_init(&sm.sp_done[i], 1);
       mbar_init(&sm.pd_ready[i], kGroupThreads);
       mbar_init(&sm.pd_free[i], 1);
@@ -175,25 +179,26 @@ __global__ void __launch_bounds__(kDkvThreads, 1) fine_bwd_dkv_kernel(const __gr
   // every barrier belongs to one buffer (stage = warpgroup = pair parity) and the round after the
   // awaited one cannot start before the waiter has moved on.
   const int pairs = (n + 1) >> 1;
-  if (warp == 9) {
-    // ------------------------------------------------------------ producer: TMA loads
+  if (warp == 9 || warp == 10) {
+    // ------------------------------------------------------------ producers: TMA loads
     if (lane == 0 && n > 0) {
-      mbar_expect_tx(&sm.kv_full, 2 * kTileBytes);
-      tma_load_tile(sm.k, &p.k_map, &sm.kv_full, head, kvb);
-      tma_load_tile(sm.v, &p.v_map, &sm.kv_full, head, kvb);
+      const bool is_q = warp == 9;
+      if (is_q) {
+        mbar_expect_tx(&sm.kv_full, 2 * kTileBytes);
+        tma_load_tile(sm.k, &p.k_map, &sm.kv_full, head, kvb);
+        tma_load_tile(sm.v, &p.v_map, &sm.kv_full, head, kvb);
+      }
+      const CUtensorMap* map = is_q ? &p.q_half_map : &p.do_half_map;
       for (int i = 0; i < pairs; ++i) {
         const int stage = i & 1, count = (2 * i + 1 < n) ? 2 : 1;
-        // The stage was last read by the gradient products of pair i - 2.
-        if (i >= 2) mbar_wait(&sm.qd_free[stage], ((i >> 1) - 1) & 1, abort_flag, p.status, 25);
-        mbar_expect_tx(&sm.qd_full[stage], count * 2 * kTileBytes);
+        uint64_t* full = is_q ? &sm.q_full[stage] : &sm.do_full[stage];
+        uint8_t* dst = is_q ? sm.q[stage] : sm.d_o[stage];
+        // The stage was last read by a gradient product of pair i - 2.
+        if (i >= 2) mbar_wait(is_q ? &sm.q_free[stage] : &sm.do_free[stage], ((i >> 1) - 1) & 1, abort_flag, p.status, 25);
+        mbar_expect_tx(full, count * kTileBytes);
         for (int t = 0; t < count; ++t) {
           const int q_block = cursor.next();
-          for (int h = 0; h < 2; ++h) {
-            tma_load_half(sm.q[stage] + h * kTileBytes + t * kHalfTileBytes, &p.q_half_map, &sm.qd_full[stage], head,
-                          q_block, h);
-            tma_load_half(sm.d_o[stage] + h * kTileBytes + t * kHalfTileBytes, &p.do_half_map, &sm.qd_full[stage], head,
-                          q_block, h);
-          }
+          for (int h = 0; h < 2; ++h) tma_load_half(dst + h * kTileBytes + t * kHalfTileBytes, map, full, head, q_block, h);
         }
       }
     }
@@ -209,9 +214,11 @@ __global__ void __launch_bounds__(kDkvThreads, 1) fine_bwd_dkv_kernel(const __gr
       constexpr uint32_t kPairLo = kPairBytes >> 4, kBufLo = kTileBytes >> 4;
       auto scores = [&](int j) {
         const int b = j & 1;
-        mbar_wait(&sm.qd_full[b], (j >> 1) & 1, abort_flag, p.status, 26);
+        mbar_wait(&sm.q_full[b], (j >> 1) & 1, abort_flag, p.status, 26);
         tc_fence_after();
         issue_pair_scores(tmem + b * 128, q_lo0 + b * kPairLo, k_lo);
+        mbar_wait(&sm.do_full[b], (j >> 1) & 1, abort_flag, p.status, 26);
+        tc_fence_after();
         issue_pair_scores(tmem + b * 128 + 64, do_lo0 + b * kPairLo, v_lo);
         umma_commit(&sm.sp_done[b]);
       };
@@ -222,9 +229,10 @@ __global__ void __launch_bounds__(kDkvThreads, 1) fine_bwd_dkv_kernel(const __gr
         mbar_wait(&sm.pd_ready[b], (j >> 1) & 1, abort_flag, p.status, 29);
         tc_fence_after();
         const bool two = 2 * j + 1 < n;
-        issue_pair_grad(tmem + kColDv, do_mn_lo0 + b * kPairLo, pt_lo0 + b * kBufLo, two, j > 0);   // dV^T += dO^T P
-        issue_pair_grad(tmem + kColDk, q_mn_lo0 + b * kPairLo, dst_lo0 + b * kBufLo, two, j > 0);   // dK^T += Q^T dS
-        umma_commit(&sm.qd_free[b]);
+        issue_pair_grad(tmem + kColDk, q_mn_lo0 + b * kPairLo, dst_lo0 + b * kBufLo, two, j > 0);  // dK^T += Q^T dS
+        umma_commit(&sm.q_free[b]);
+        issue_pair_grad(tmem + kColDv, do_mn_lo0 + b * kPairLo, pt_lo0 + b * kBufLo, two, j > 0);  // dV^T += dO^T P
+        umma_commit(&sm.do_free[b]);
         umma_commit(&sm.pd_free[b]);
       };
       mbar_wait(&sm.kv_full, 0, abort_flag, p.status, 21);

@@ -27,7 +27,7 @@ namespace {
 
 constexpr int kGroupThreads = 128;  // one score-math warpgroup
 constexpr int kMathThreads = 256;   // warps 0..3: warpgroup 0 (even pairs), warps 4..7: warpgroup 1 (odd pairs)
-constexpr int kThreads = 320;       // warp 8: tcgen05.mma issue, warp 9: TMA loads
+constexpr int kThreads = 352;       // warp 8: tcgen05.mma issue, warps 9 / 10: TMA loads of Q, dO, K / of V
 constexpr int kTmemCols = 512;      // per warpgroup g: S^T [128g, 128g+64)  dP^T [128g+64, 128g+128);  dQ^T [256,320)
 constexpr uint32_t kColDq = 256;
 constexpr int kKStages = 3;
@@ -129,36 +129,32 @@ __global__ void __launch_bounds__(kThreads, 1) fine_bwd_dq_kernel(const __grid_c
   // every barrier belongs to one buffer and the round after the awaited one cannot start before
   // the waiter has moved on.
   const int pairs = (n + 1) >> 1;
-  if (warp == 9) {
-    // ------------------------------------------------------------ producer: TMA loads
+  if (warp == 9 || warp == 10) {
+    // ------------------------------------------------------------ producers: TMA loads
+    // K and V have a producer warp each: V stages are released after dP^T, K stages only after
+    // the dQ product, and one in-order loop would hold each load behind the other's wait.
     if (lane == 0 && n > 0) {
-      mbar_expect_tx(&sm.qdo_full, 2 * kTileBytes);
-      tma_load_tile(sm.q, &p.q_map, &sm.qdo_full, head, qb);
-      tma_load_tile(sm.d_o, &p.do_map, &sm.qdo_full, head, qb);
-      int ks = 0, vs = 0;
-      uint32_t k_round = 0, v_round = 0;  // parity of the release awaited before refilling the stage
+      const bool is_k = warp == 9;
+      if (is_k) {
+        mbar_expect_tx(&sm.qdo_full, 2 * kTileBytes);
+        tma_load_tile(sm.q, &p.q_map, &sm.qdo_full, head, qb);
+        tma_load_tile(sm.d_o, &p.do_map, &sm.qdo_full, head, qb);
+      }
+      const CUtensorMap* map = is_k ? &p.k_half_map : &p.v_half_map;
+      const int stages = is_k ? kKStages : kVStages;
+      int stage = 0;
+      uint32_t round = 0;  // parity of the release awaited before refilling the stage
       for (int i = 0; i < pairs; ++i) {
         const int count = (2 * i + 1 < n) ? 2 : 1;
-        // V stages are released first (after dP^T), K stages after the dQ product.
-        if (i >= kVStages) mbar_wait(&sm.v_free[vs], v_round, abort_flag, p.status, 12);
-        mbar_expect_tx(&sm.v_full[vs], count * kTileBytes);
+        uint64_t* full = is_k ? &sm.k_full[stage] : &sm.v_full[stage];
+        uint8_t* dst = is_k ? sm.k[stage] : sm.v[stage];
+        if (i >= stages) mbar_wait(is_k ? &sm.k_free[stage] : &sm.v_free[stage], round, abort_flag, p.status, 12);
+        mbar_expect_tx(full, count * kTileBytes);
         for (int t = 0; t < count; ++t)
-          for (int h = 0; h < 2; ++h)
-            tma_load_half(sm.v[vs] + h * kTileBytes + t * kHalfTileBytes, &p.v_half_map, &sm.v_full[vs], head,
-                          list[2 * i + t], h);
-        if (i >= kKStages) mbar_wait(&sm.k_free[ks], k_round, abort_flag, p.status, 11);
-        mbar_expect_tx(&sm.k_full[ks], count * kTileBytes);
-        for (int t = 0; t < count; ++t)
-          for (int h = 0; h < 2; ++h)
-            tma_load_half(sm.k[ks] + h * kTileBytes + t * kHalfTileBytes, &p.k_half_map, &sm.k_full[ks], head,
-                          list[2 * i + t], h);
-        if (++vs == kVStages) {
-          vs = 0;
-          if (i >= kVStages) v_round ^= 1;
-        }
-        if (++ks == kKStages) {
-          ks = 0;
-          if (i >= kKStages) k_round ^= 1;
+          for (int h = 0; h < 2; ++h) tma_load_half(dst + h * kTileBytes + t * kHalfTileBytes, map, full, head, list[2 * i + t], h);
+        if (++stage == stages) {
+          stage = 0;
+          if (i >= stages) round ^= 1;
         }
       }
     }

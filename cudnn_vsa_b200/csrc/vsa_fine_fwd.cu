@@ -11,19 +11,20 @@
 // 128-row K-major operand ([dim half][tile][row][128 B], four 8 KiB TMA boxes); V tiles stay
 // separate and are read MN-major.
 //
-// The list is split between two softmax warpgroups: even pairs belong to warpgroup 0, odd pairs
-// to warpgroup 1, each with its own S / P buffer, its own O accumulator and its own running
-// maximum and sum (tensor memory: S0 S1 O0 O1, 4 x 128 columns, one CTA per SM).  A single thread
-// issues every MMA in the fixed order  ... P V(i)  Q K(i+2)  P V(i+1)  Q K(i+3) ...  so while one
-// warpgroup exponentiates pair i+1 the tensor core runs the products of its neighbours: the
-// exponentials (MUFU, 16 per clock per SM) and the MMAs overlap by construction instead of by
-// chance.  (Two independent CTAs per SM fall into lock-step: the tensor pipe serves their MMAs
-// alternately, both reach their softmax together and the two units take turns idling.)
-// Within a warpgroup two threads share a query row (one KV block of the pair each); the running
-// maximum is raised only when it grew by more than 2^8, and only then do the two threads of a row
-// rescale that row of their O in tensor memory - no CTA-wide synchronisation in the loop.
-// The epilogue combines the two partial results, writes the normalised fine output in slot
-// order, the natural-log LSE and - when a row map is given - the merged result
+// S has three buffers in tensor memory (S0 S1 S2 O, 4 x 128 columns, one CTA per SM) and a single
+// thread issues every MMA in the fixed order  ... P V(i)  Q K(i+3)  P V(i+1)  Q K(i+4) ...  so
+// the softmax of the next pairs runs under the products of their neighbours and neither side
+// waits for a hand-off.  What bounds a pair outside
+// the tensor core is the exponential unit (16 per clock per SM: 512 cycles for the 8192 scores
+// of a pair), so all 256 softmax threads work on every pair - four threads per query row, 32
+// scores each; the two warpgroups exchange the row maxima through shared memory - instead of
+// alternating pairs, which would put two pairs' exponentials in flight at once and double the
+// latency of each.  (Two independent CTAs per SM fall into lock-step instead: the tensor pipe
+// serves their MMAs alternately, both reach their softmax together and the units take turns
+// idling.)  The running maximum is raised only when it grew by more than 2^8, and only then do
+// the threads of a row rescale that row of O in tensor memory, after the one product that may
+// still be accumulating into it has finished.  The epilogue writes the normalised fine output
+// in slot order, the natural-log LSE and - when a row map is given - the merged result
 // `fine + gate * coarse[block]` straight into the caller's row order, which replaces the
 // reference's separate restore and gate-add passes (reference vsa_core.py:15-20,
 // vsa_kernels.py:191-201, vsa.py:111-117).
@@ -34,11 +35,11 @@ namespace vsa {
 
 namespace {
 
-constexpr int kGroupThreads = 128;    // one softmax warpgroup
-constexpr int kSoftmaxThreads = 256;  // warps 0..3: warpgroup 0 (even pairs), warps 4..7: warpgroup 1 (odd pairs)
-constexpr int kThreads = 320;         // warp 8: tcgen05.mma issue, warp 9: TMA loads
-constexpr int kTmemCols = 512;        // S0 / P0 [0,128)  S1 / P1 [128,256)  O0 [256,384)  O1 [384,512)
-constexpr uint32_t kColO = 256;
+constexpr int kSoftmaxThreads = 256;  // warps 0..7: softmax and epilogue (four threads per query row)
+constexpr int kThreads = 352;         // warp 8: tcgen05.mma issue, warp 9: TMA loads of Q and K, warp 10: of V
+constexpr int kTmemCols = 512;        // S / P buffers b = 0..2 at [128 b, 128 b + 128)   O [384,512)
+constexpr int kSBuffers = 3;
+constexpr uint32_t kColO = 384;
 constexpr int kStages = 3;            // pair stages of K and of V (32 KiB each)
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kRescaleThreshold = 8.0f;  // log2 units
@@ -47,9 +48,10 @@ struct FwdSmem {  // placed at a 1024-byte aligned address; every tile offset is
   uint8_t q[kTileBytes];
   uint8_t k[kStages][2 * kTileBytes];  // [dim half][tile of the pair][row][128 B]
   uint8_t v[kStages][2][kTileBytes];   // [tile of the pair][dim half][row][128 B]
-  float m_part[2][kBlock], l_part[2][kBlock];  // per warpgroup and query row (epilogue)
+  float m_part[2][2][kBlock];          // [pair parity][warpgroup][query row]: maximum over the warpgroup's columns
+  float l_part[2][kBlock];             // [warpgroup][query row]: partial softmax denominators (epilogue)
   uint64_t q_full, k_full[kStages], v_full[kStages], k_free[kStages], v_free[kStages];
-  uint64_t s_done[2], p_ready[2], o_final;
+  uint64_t s_done[kSBuffers], p_ready[kSBuffers], o_done[2];
   uint32_t tmem_base;
   int abort_flag;
 };
@@ -93,8 +95,8 @@ __global__ void __launch_bounds__(kThreads, 1) fine_fwd_kernel(const __grid_cons
   FwdSmem& sm = *reinterpret_cast<FwdSmem*>(smem_raw + ((1024 - (smem_u32(smem_raw) & 1023)) & 1023));
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int qb = blockIdx.x, head = blockIdx.y;
-  const int group = (warp >> 2) & 1;              // softmax warpgroup (warps 0..7 only)
-  const int row = (warp & 3) * 16 + (lane & 15);  // query row inside the block (softmax role)
+  const int group = (warp >> 2) & 1;              // which 32 keys of a KV block (softmax warps 0..7)
+  const int row = (warp & 3) * 16 + (lane & 15);  // query row inside the block
   const int half = lane >> 4;                     // which KV block of the pair
   const int n = p.counts[static_cast<long long>(head) * p.count_head_stride + qb];
   const int32_t* list = p.indices + static_cast<long long>(head) * p.index_head_stride +
@@ -108,11 +110,12 @@ __global__ void __launch_bounds__(kThreads, 1) fine_fwd_kernel(const __grid_cons
       mbar_init(&sm.k_free[i], 1);
       mbar_init(&sm.v_free[i], 1);
     }
-    for (int i = 0; i < 2; ++i) {
+    for (int i = 0; i < kSBuffers; ++i) {
       mbar_init(&sm.s_done[i], 1);
-      mbar_init(&sm.p_ready[i], kGroupThreads);
+      mbar_init(&sm.p_ready[i], kSoftmaxThreads);
     }
-    mbar_init(&sm.o_final, 1);
+    mbar_init(&sm.o_done[0], 1);
+    mbar_init(&sm.o_done[1], 1);
     sm.abort_flag = 0;
     fence_barrier_init();
     tma_prefetch_desc(&p.q_map);
@@ -131,7 +134,7 @@ __global__ void __launch_bounds__(kThreads, 1) fine_fwd_kernel(const __grid_cons
   volatile int* abort_flag = &sm.abort_flag;
 
   const float sl2 = p.scale * kLog2e;
-  float m_ref = -INFINITY;  // running reference maximum of the raw scores (this warpgroup's pairs)
+  float m_ref = -INFINITY;  // running reference maximum of the raw scores of this query row
   float l = 0.f;            // running sum of exp2((s - m_ref) * sl2) over this thread's columns
 
   // Barrier discipline: a barrier is only ever waited on for its NEWEST commit or arrival round
@@ -140,7 +143,10 @@ __global__ void __launch_bounds__(kThreads, 1) fine_fwd_kernel(const __grid_cons
   // barrier cannot start before the waiter has moved on.
   const int pairs = (n + 1) >> 1;
   if (warp == 9) {
-    // ------------------------------------------------------------ producer: TMA loads
+    // ------------------------------------------------------------ producer of Q and K
+    // K and V have a producer each: their stages are released at different times (K pairs are
+    // consumed three pairs ahead of V pairs), and one in-order loop would hold every K load
+    // behind the wait for the preceding V stage.
     if (lane == 0 && n > 0) {
       mbar_expect_tx(&sm.q_full, kTileBytes);
       tma_load_tile(sm.q, &p.q_map, &sm.q_full, head, qb);
@@ -154,6 +160,15 @@ __global__ void __launch_bounds__(kThreads, 1) fine_fwd_kernel(const __grid_cons
           for (int h = 0; h < 2; ++h)
             tma_load_half(sm.k[stage] + h * kTileBytes + t * kHalfTileBytes, &p.k_half_map, &sm.k_full[stage], head,
                           list[2 * i + t], h);
+      }
+    }
+  } else if (warp == 10) {
+    // ------------------------------------------------------------ producer of V
+    if (lane == 0 && n > 0) {
+      for (int i = 0; i < pairs; ++i) {
+        const int count = (2 * i + 1 < n) ? 2 : 1;
+        const int stage = i % kStages;
+        const uint32_t reuse = ((i / kStages) - 1) & 1;
         if (i >= kStages) mbar_wait(&sm.v_free[stage], reuse, abort_flag, p.status, 10);
         mbar_expect_tx(&sm.v_full[stage], count * kTileBytes);
         for (int t = 0; t < count; ++t) tma_load_tile(sm.v[stage][t], &p.v_map, &sm.v_full[stage], head, list[2 * i + t]);
@@ -168,13 +183,14 @@ __global__ void __launch_bounds__(kThreads, 1) fine_fwd_kernel(const __grid_cons
       const uint32_t k_lo0 = umma_desc_lo(smem_u32(sm.k[0]), 16);
       const uint32_t v_lo0 = umma_desc_lo(smem_u32(sm.v[0][0]), kHalfTileBytes);
       constexpr uint32_t kStageLo = (2 * kTileBytes) >> 4;
-      int k_stage = 0, v_stage = 0;       // stage of the next S product / the next P V product
-      uint32_t k_phase = 0, v_phase = 0;  // parity of that stage's current fill
+      static_assert(kStages == kSBuffers, "one counter walks the K stages and the S buffers");
+      int k_stage = 0, v_stage = 0;       // stage (= S buffer) of the next S product / the next P V product
+      uint32_t k_phase = 0, v_phase = 0;  // parity of that stage's current fill (= round of the S buffer)
       auto qk = [&](int j) {
         mbar_wait(&sm.k_full[k_stage], k_phase, abort_flag, p.status, 2);
         tc_fence_after();
-        issue_qk(tmem + (j & 1) * 128, q_lo, k_lo0 + k_stage * kStageLo, 2 * j + 1 < n);
-        umma_commit(&sm.s_done[j & 1]);
+        issue_qk(tmem + k_stage * 128, q_lo, k_lo0 + k_stage * kStageLo, 2 * j + 1 < n);
+        umma_commit(&sm.s_done[k_stage]);
         umma_commit(&sm.k_free[k_stage]);
         if (++k_stage == kStages) {
           k_stage = 0;
@@ -182,95 +198,104 @@ __global__ void __launch_bounds__(kThreads, 1) fine_fwd_kernel(const __grid_cons
         }
       };
       mbar_wait(&sm.q_full, 0, abort_flag, p.status, 1);
-      qk(0);
-      if (pairs > 1) qk(1);
+      for (int j = 0; j < kSBuffers && j < pairs; ++j) qk(j);
       for (int i = 0; i < pairs; ++i) {
-        mbar_wait(&sm.p_ready[i & 1], (i >> 1) & 1, abort_flag, p.status, 9);
+        mbar_wait(&sm.p_ready[v_stage], v_phase, abort_flag, p.status, 9);
         mbar_wait(&sm.v_full[v_stage], v_phase, abort_flag, p.status, 6);
         tc_fence_after();
-        issue_pv(tmem + kColO + (i & 1) * 128, tmem + (i & 1) * 128, v_lo0 + v_stage * kStageLo, 2 * i + 1 < n, i >= 2);
+        issue_pv(tmem + kColO, tmem + v_stage * 128, v_lo0 + v_stage * kStageLo, 2 * i + 1 < n, i > 0);
+        umma_commit(&sm.o_done[i & 1]);
         umma_commit(&sm.v_free[v_stage]);
         if (++v_stage == kStages) {
           v_stage = 0;
           v_phase ^= 1;
         }
-        // The next S product of this warpgroup overwrites P; MMAs of one thread run in issue
+        // The S product of pair i + 3 overwrites P of pair i; MMAs of one thread run in issue
         // order, so it starts after the P V product above has read its operand.
-        if (i + 2 < pairs) qk(i + 2);
+        if (i + kSBuffers < pairs) qk(i + kSBuffers);
       }
-      umma_commit(&sm.o_final);
     }
   } else {
-    // ------------------------------------------------------------ softmax warpgroups
-    const uint32_t tmem_s = tmem + lane_base + group * 128;
-    const uint32_t tmem_o = tmem + lane_base + kColO + group * 128;
+    // ------------------------------------------------------------ softmax warps
+    // Thread (row, half, group) owns keys [32 group, 32 group + 32) of KV block `half` of the pair.
     // The valid length of a tile comes from two dependent global loads (list, then sizes); they
-    // are issued one round ahead so their latency never sits in the loop.
+    // are issued one pair ahead so their latency never sits in the loop.
     int size_next = kBlock;
-    if (p.kv_sizes != nullptr && 2 * group + half < n) size_next = p.kv_sizes[list[2 * group + half]];
-    for (int i = group; i < pairs; i += 2) {
+    if (p.kv_sizes != nullptr && half < n) size_next = p.kv_sizes[list[half]];
+    int buf = 0;           // S buffer of pair i
+    uint32_t buf_round = 0;  // parity of that buffer's current use
+    for (int i = 0; i < pairs; ++i) {
       const bool present = 2 * i + half < n;  // an odd list ends with half a pair
-      const int kv_size = present ? size_next : 0;
-      if (p.kv_sizes != nullptr && 2 * i + 4 + half < n) size_next = p.kv_sizes[list[2 * i + 4 + half]];
-      // The commit also covers every earlier MMA, so this warpgroup's O is stable until p_ready.
-      mbar_wait(&sm.s_done[group], (i >> 1) & 1, abort_flag, p.status, 3);
+      const int kv_left = (present ? size_next : 0) - 32 * group;  // valid keys among this thread's 32
+      if (p.kv_sizes != nullptr && 2 * i + 2 + half < n) size_next = p.kv_sizes[list[2 * i + 2 + half]];
+      const uint32_t tmem_s = tmem + lane_base + buf * 128;
+      mbar_wait(&sm.s_done[buf], buf_round, abort_flag, p.status, 3);
       tc_fence_after();
-      uint32_t s_bits[64];
-      VSA_TMEM_LD_16x32bx2_X32(s_bits, tmem_s, 64);
-      VSA_TMEM_LD_16x32bx2_X32((s_bits + 32), tmem_s + 32, 64);
+      uint32_t s_bits[32];
+      VSA_TMEM_LD_16x32bx2_X32(s_bits, tmem_s + 32 * group, 64);
       tmem_wait_ld();
-      float s[64];
-      if (kv_size < kBlock) {
+      float s[32];
+      if (kv_left < 32) {
 #pragma unroll
-        for (int e = 0; e < 64; ++e) s[e] = e < kv_size ? __uint_as_float(s_bits[e]) : -INFINITY;
+        for (int e = 0; e < 32; ++e) s[e] = e < kv_left ? __uint_as_float(s_bits[e]) : -INFINITY;
       } else {
 #pragma unroll
-        for (int e = 0; e < 64; ++e) s[e] = __uint_as_float(s_bits[e]);
+        for (int e = 0; e < 32; ++e) s[e] = __uint_as_float(s_bits[e]);
       }
       // Four independent chains keep the dependent-latency path short.
       float m4[4] = {s[0], s[1], s[2], s[3]};
 #pragma unroll
-      for (int e = 4; e < 64; ++e) m4[e & 3] = fmaxf(m4[e & 3], s[e]);
+      for (int e = 4; e < 32; ++e) m4[e & 3] = fmaxf(m4[e & 3], s[e]);
       float m_pair = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
       m_pair = fmaxf(m_pair, __shfl_xor_sync(0xffffffffu, m_pair, 16));
+      // The other warpgroup holds the other 64 scores of this row.  Every S read of the pair
+      // precedes the barrier, so P may be written over S after it.
+      if (half == 0) sm.m_part[i & 1][group][row] = m_pair;
+      named_barrier(1, kSoftmaxThreads);
+      m_pair = fmaxf(m_pair, sm.m_part[i & 1][group ^ 1][row]);
       const float m_new = fmaxf(m_ref, m_pair);
-      // Raise the reference maximum only when it moved by more than 2^8; both threads of a row
-      // see the same m_pair, so they decide alike.
+      // Raise the reference maximum only when it moved by more than 2^8; the four threads of a
+      // row see the same m_pair, so they decide alike.
       const bool raise = (m_new > m_ref) && (m_ref == -INFINITY || (m_new - m_ref) * sl2 > kRescaleThreshold);
       float alpha = 1.f;
       if (raise) {
         alpha = (m_ref == -INFINITY) ? 0.f : fast_exp2((m_ref - m_new) * sl2);
         m_ref = m_new;
       }
-      if (__any_sync(0xffffffffu, raise && i >= 2)) {
-        // Rare: this thread scales its 64 columns of its row of O.
+      if (__any_sync(0xffffffffu, raise && i > 0)) {
+        // Rare: this thread scales its 32 columns of its row of O, once the P V product of the
+        // previous pair - the only one that may still be accumulating - has finished.
+        mbar_wait(&sm.o_done[(i - 1) & 1], ((i - 1) >> 1) & 1, abort_flag, p.status, 5);
+        tc_fence_after();
+        uint32_t o_bits[32];
+        const uint32_t addr = tmem + lane_base + kColO + 32 * group;
+        VSA_TMEM_LD_16x32bx2_X32(o_bits, addr, 64);
+        tmem_wait_ld();
 #pragma unroll
-        for (int c = 0; c < 2; ++c) {
-          uint32_t o_bits[32];
-          VSA_TMEM_LD_16x32bx2_X32(o_bits, tmem_o + c * 32, 64);
-          tmem_wait_ld();
-#pragma unroll
-          for (int e = 0; e < 32; ++e) o_bits[e] = __float_as_uint(__uint_as_float(o_bits[e]) * alpha);
-          VSA_TMEM_ST_16x32bx2_X32(o_bits, tmem_o + c * 32, 64);
-        }
+        for (int e = 0; e < 32; ++e) o_bits[e] = __float_as_uint(__uint_as_float(o_bits[e]) * alpha);
+        VSA_TMEM_ST_16x32bx2_X32(o_bits, addr, 64);
       }
       const float m_use = (m_ref == -INFINITY) ? 0.f : m_ref * sl2;
-      uint32_t packed[32];
+      uint32_t packed[16];
       float sum4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-      for (int e = 0; e < 64; e += 2) {
+      for (int e = 0; e < 32; e += 2) {
         const float p0 = fast_exp2(fmaf(s[e], sl2, -m_use));
         const float p1 = fast_exp2(fmaf(s[e + 1], sl2, -m_use));
         packed[e >> 1] = pack_bf16(p0, p1);
         sum4[(e >> 1) & 3] += p0 + p1;
       }
       l = l * alpha + ((sum4[0] + sum4[1]) + (sum4[2] + sum4[3]));
-      // P over the first 64 columns of S: keys of the pair's first block in columns [0,32), of
-      // its second block in [32,64).  Every S read of this warp has completed (wait::ld above).
-      VSA_TMEM_ST_16x32bx2_X32(packed, tmem_s, 32);
+      // P over the first 64 columns of S, two keys per column: block `half` of the pair in
+      // columns [32 half, 32 half + 32), this thread's keys in the 16 columns from 16 group.
+      VSA_TMEM_ST_16x32bx2_X16(packed, tmem_s + 16 * group, 32);
       tmem_wait_st();
       tc_fence_before();
-      mbar_arrive(&sm.p_ready[group]);
+      mbar_arrive(&sm.p_ready[buf]);
+      if (++buf == kSBuffers) {
+        buf = 0;
+        buf_round ^= 1;
+      }
     }
   }
 
@@ -278,27 +303,17 @@ __global__ void __launch_bounds__(kThreads, 1) fine_fwd_kernel(const __grid_cons
   if (warp < 8) {
     const long long width = static_cast<long long>(p.heads) * kDim;
     l += __shfl_xor_sync(0xffffffffu, l, 16);
-    if (half == 0) {
-      sm.m_part[group][row] = m_ref;
-      sm.l_part[group][row] = l;
-    }
+    if (half == 0) sm.l_part[group][row] = l;
     if (n > 0) {
-      mbar_wait(&sm.o_final, 0, abort_flag, p.status, 7);
+      mbar_wait(&sm.o_done[(pairs - 1) & 1], ((pairs - 1) >> 1) & 1, abort_flag, p.status, 7);
       tc_fence_after();
     }
     named_barrier(1, kSoftmaxThreads);
-    // Combine the two warpgroups' partial softmax results of this row.
-    const float m0 = sm.m_part[0][row], m1 = sm.m_part[1][row];
-    const float l0 = sm.l_part[0][row], l1 = sm.l_part[1][row];
-    const float m_all = fmaxf(m0, m1);
-    const float a0 = l0 > 0.f ? fast_exp2((m0 - m_all) * sl2) : 0.f;
-    const float a1 = l1 > 0.f ? fast_exp2((m1 - m_all) * sl2) : 0.f;
-    const float l_all = l0 * a0 + l1 * a1;
+    const float l_all = sm.l_part[0][row] + sm.l_part[1][row];
     const float inv_l = l_all > 0.f ? 1.f / l_all : 0.f;
-    const float w0 = a0 * inv_l, w1 = a1 * inv_l;
     const long long slot = static_cast<long long>(qb) * kBlock + row;
     if (half == 0 && group == 0)
-      p.lse[static_cast<long long>(head) * p.q_slots + slot] = l_all > 0.f ? m_all * p.scale + logf(l_all) : -INFINITY;
+      p.lse[static_cast<long long>(head) * p.q_slots + slot] = l_all > 0.f ? m_ref * p.scale + logf(l_all) : -INFINITY;
     // Thread = (query row, 32 head dims): 64 contiguous bytes of one output row.
     const int dim0 = half * 64 + group * 32;
     const long long col = static_cast<long long>(head) * kDim + dim0;
@@ -316,18 +331,16 @@ __global__ void __launch_bounds__(kThreads, 1) fine_fwd_kernel(const __grid_cons
     }
     uint4* o_dst = reinterpret_cast<uint4*>(p.o_slots + slot * width + col);
     uint4* out_dst = (kMerge && out_row >= 0) ? reinterpret_cast<uint4*>(p.out + out_row * width + col) : nullptr;
-    uint32_t o0[32] = {}, o1[32] = {};
-    // A warpgroup without pairs never wrote its accumulator: its columns are not read (the
-    // conditions are uniform over the CTA, as the warp-wide loads require).
-    if (pairs > 0) VSA_TMEM_LD_16x32bx2_X32(o0, tmem + lane_base + kColO + group * 32, 64);
-    if (pairs > 1) VSA_TMEM_LD_16x32bx2_X32(o1, tmem + lane_base + kColO + 128 + group * 32, 64);
-    tmem_wait_ld();
+    uint32_t o_bits[32] = {};
+    if (n > 0) {
+      VSA_TMEM_LD_16x32bx2_X32(o_bits, tmem + lane_base + kColO + group * 32, 64);
+      tmem_wait_ld();
+    }
 #pragma unroll
     for (int v4 = 0; v4 < 4; ++v4) {
       float o[8];
 #pragma unroll
-      for (int e = 0; e < 8; ++e)
-        o[e] = __uint_as_float(o0[v4 * 8 + e]) * w0 + __uint_as_float(o1[v4 * 8 + e]) * w1;
+      for (int e = 0; e < 8; ++e) o[e] = __uint_as_float(o_bits[v4 * 8 + e]) * inv_l;
       o_dst[v4] = make_uint4(pack_bf16(o[0], o[1]), pack_bf16(o[2], o[3]), pack_bf16(o[4], o[5]), pack_bf16(o[6], o[7]));
       if (kMerge && out_dst != nullptr) {
         if (gate != nullptr) {
