@@ -197,6 +197,19 @@ VSA_DEVICE void umma_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t desc_b, uint3
       : "memory");
 }
 
+// True in exactly one lane of a converged warp.  Code that the whole warp runs with uniform
+// control flow and that only predicates its side effects with this flag keeps its address
+// arithmetic warp-uniform, unlike a `lane == 0` branch.
+VSA_DEVICE bool elect_one() {
+  uint32_t pred;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "elect.sync _|p, 0xffffffff;\n\t"
+      "selp.b32 %0, 1, 0, p;\n\t}"
+      : "=r"(pred));
+  return pred != 0;
+}
+
 // Lean issue path.  The thread that issues the MMAs is alone in its warp, so every scalar
 // instruction between two MMAs costs its full latency: building two 64-bit descriptors per MMA
 // (about twenty dependent instructions) takes longer than the 64 cycles an M64/N128 MMA runs

@@ -204,7 +204,10 @@ __global__ void __launch_bounds__(kDkvThreads, 1) fine_bwd_dkv_kernel(const __gr
     }
   } else if (warp == 8) {
     // ------------------------------------------------------------ issuer: MMAs
-    if (lane == 0 && n > 0) {
+    // The whole warp walks the loop (uniform control flow and addresses); one elected lane
+    // issues the MMAs and commits.
+    if (n > 0) {
+      const bool leader = elect_one();
       const uint32_t k_lo = umma_desc_lo(smem_u32(sm.k), 16), v_lo = umma_desc_lo(smem_u32(sm.v), 16);
       const uint32_t q_lo0 = umma_desc_lo(smem_u32(sm.q[0]), 16), do_lo0 = umma_desc_lo(smem_u32(sm.d_o[0]), 16);
       const uint32_t q_mn_lo0 = umma_desc_lo(smem_u32(sm.q[0]), kTileBytes);
@@ -216,11 +219,13 @@ __global__ void __launch_bounds__(kDkvThreads, 1) fine_bwd_dkv_kernel(const __gr
         const int b = j & 1;
         mbar_wait(&sm.q_full[b], (j >> 1) & 1, abort_flag, p.status, 26);
         tc_fence_after();
-        issue_pair_scores(tmem + b * 128, q_lo0 + b * kPairLo, k_lo);
+        if (leader) issue_pair_scores(tmem + b * 128, q_lo0 + b * kPairLo, k_lo);
         mbar_wait(&sm.do_full[b], (j >> 1) & 1, abort_flag, p.status, 26);
         tc_fence_after();
-        issue_pair_scores(tmem + b * 128 + 64, do_lo0 + b * kPairLo, v_lo);
-        umma_commit(&sm.sp_done[b]);
+        if (leader) {
+          issue_pair_scores(tmem + b * 128 + 64, do_lo0 + b * kPairLo, v_lo);
+          umma_commit(&sm.sp_done[b]);
+        }
       };
       auto grads = [&](int j) {
         const int b = j & 1;
@@ -229,11 +234,13 @@ __global__ void __launch_bounds__(kDkvThreads, 1) fine_bwd_dkv_kernel(const __gr
         mbar_wait(&sm.pd_ready[b], (j >> 1) & 1, abort_flag, p.status, 29);
         tc_fence_after();
         const bool two = 2 * j + 1 < n;
-        issue_pair_grad(tmem + kColDk, q_mn_lo0 + b * kPairLo, dst_lo0 + b * kBufLo, two, j > 0);  // dK^T += Q^T dS
-        umma_commit(&sm.q_free[b]);
-        issue_pair_grad(tmem + kColDv, do_mn_lo0 + b * kPairLo, pt_lo0 + b * kBufLo, two, j > 0);  // dV^T += dO^T P
-        umma_commit(&sm.do_free[b]);
-        umma_commit(&sm.pd_free[b]);
+        if (leader) {
+          issue_pair_grad(tmem + kColDk, q_mn_lo0 + b * kPairLo, dst_lo0 + b * kBufLo, two, j > 0);  // dK^T += Q^T dS
+          umma_commit(&sm.q_free[b]);
+          issue_pair_grad(tmem + kColDv, do_mn_lo0 + b * kPairLo, pt_lo0 + b * kBufLo, two, j > 0);  // dV^T += dO^T P
+          umma_commit(&sm.do_free[b]);
+          umma_commit(&sm.pd_free[b]);
+        }
       };
       mbar_wait(&sm.kv_full, 0, abort_flag, p.status, 21);
       scores(0);
@@ -244,7 +251,7 @@ __global__ void __launch_bounds__(kDkvThreads, 1) fine_bwd_dkv_kernel(const __gr
         if (i + 2 < pairs) scores(i + 2);
         if (i + 3 < pairs) scores(i + 3);
       }
-      umma_commit(&sm.dkv_final);
+      if (leader) umma_commit(&sm.dkv_final);
     }
   } else {
     // ------------------------------------------------------------ score math warpgroups

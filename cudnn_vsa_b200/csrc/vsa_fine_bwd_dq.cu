@@ -160,7 +160,10 @@ __global__ void __launch_bounds__(kThreads, 1) fine_bwd_dq_kernel(const __grid_c
     }
   } else if (warp == 8) {
     // ------------------------------------------------------------ issuer: MMAs
-    if (lane == 0 && n > 0) {
+    // The whole warp walks the loop (uniform control flow and addresses); one elected lane
+    // issues the MMAs and commits.
+    if (n > 0) {
+      const bool leader = elect_one();
       const uint32_t q_lo = umma_desc_lo(smem_u32(sm.q), 16);
       const uint32_t do_lo = umma_desc_lo(smem_u32(sm.d_o), 16);
       const uint32_t k_lo0 = umma_desc_lo(smem_u32(sm.k[0]), 16);
@@ -174,10 +177,12 @@ __global__ void __launch_bounds__(kThreads, 1) fine_bwd_dq_kernel(const __grid_c
         mbar_wait(&sm.k_full[s_k], s_k_phase, abort_flag, p.status, 15);
         mbar_wait(&sm.v_full[s_v], s_v_phase, abort_flag, p.status, 15);
         tc_fence_after();
-        issue_scores(tmem + (j & 1) * 128, k_lo0 + s_k * kPairLo, q_lo);
-        issue_scores(tmem + (j & 1) * 128 + 64, v_lo0 + s_v * kPairLo, do_lo);
-        umma_commit(&sm.sp_done[j & 1]);
-        umma_commit(&sm.v_free[s_v]);
+        if (leader) {
+          issue_scores(tmem + (j & 1) * 128, k_lo0 + s_k * kPairLo, q_lo);
+          issue_scores(tmem + (j & 1) * 128 + 64, v_lo0 + s_v * kPairLo, do_lo);
+          umma_commit(&sm.sp_done[j & 1]);
+          umma_commit(&sm.v_free[s_v]);
+        }
         if (++s_k == kKStages) {
           s_k = 0;
           s_k_phase ^= 1;
@@ -195,13 +200,15 @@ __global__ void __launch_bounds__(kThreads, 1) fine_bwd_dq_kernel(const __grid_c
         // S^T / dP^T accumulators: they may be overwritten by pair i + 2 below.
         mbar_wait(&sm.ds_ready[i & 1], (i >> 1) & 1, abort_flag, p.status, 18);
         tc_fence_after();
-        issue_dq(tmem + kColDq, k_mn_lo0 + d_k * kPairLo, ds_lo0 + (i & 1) * kDsLo, 2 * i + 1 < n, i > 0);
-        umma_commit(&sm.k_free[d_k]);
-        umma_commit(&sm.ds_free[i & 1]);
+        if (leader) {
+          issue_dq(tmem + kColDq, k_mn_lo0 + d_k * kPairLo, ds_lo0 + (i & 1) * kDsLo, 2 * i + 1 < n, i > 0);
+          umma_commit(&sm.k_free[d_k]);
+          umma_commit(&sm.ds_free[i & 1]);
+        }
         if (++d_k == kKStages) d_k = 0;
         if (i + 2 < pairs) scores(i + 2);
       }
-      umma_commit(&sm.dq_final);
+      if (leader) umma_commit(&sm.dq_final);
     }
   } else {
     // ------------------------------------------------------------ score math warpgroups

@@ -176,7 +176,10 @@ __global__ void __launch_bounds__(kThreads, 1) fine_fwd_kernel(const __grid_cons
     }
   } else if (warp == 8) {
     // ------------------------------------------------------------ issuer: MMAs
-    if (lane == 0 && n > 0) {
+    // The whole warp walks the loop (uniform control flow and addresses); one elected lane
+    // issues the MMAs and commits.
+    if (n > 0) {
+      const bool leader = elect_one();
       // Everything the loop needs is in registers: descriptor low words, barrier addresses by
       // stage, and stage / phase counters that advance without divisions.
       const uint32_t q_lo = umma_desc_lo(smem_u32(sm.q), 16);
@@ -189,9 +192,11 @@ __global__ void __launch_bounds__(kThreads, 1) fine_fwd_kernel(const __grid_cons
       auto qk = [&](int j) {
         mbar_wait(&sm.k_full[k_stage], k_phase, abort_flag, p.status, 2);
         tc_fence_after();
-        issue_qk(tmem + k_stage * 128, q_lo, k_lo0 + k_stage * kStageLo, 2 * j + 1 < n);
-        umma_commit(&sm.s_done[k_stage]);
-        umma_commit(&sm.k_free[k_stage]);
+        if (leader) {
+          issue_qk(tmem + k_stage * 128, q_lo, k_lo0 + k_stage * kStageLo, 2 * j + 1 < n);
+          umma_commit(&sm.s_done[k_stage]);
+          umma_commit(&sm.k_free[k_stage]);
+        }
         if (++k_stage == kStages) {
           k_stage = 0;
           k_phase ^= 1;
@@ -203,9 +208,11 @@ __global__ void __launch_bounds__(kThreads, 1) fine_fwd_kernel(const __grid_cons
         mbar_wait(&sm.p_ready[v_stage], v_phase, abort_flag, p.status, 9);
         mbar_wait(&sm.v_full[v_stage], v_phase, abort_flag, p.status, 6);
         tc_fence_after();
-        issue_pv(tmem + kColO, tmem + v_stage * 128, v_lo0 + v_stage * kStageLo, 2 * i + 1 < n, i > 0);
-        umma_commit(&sm.o_done[i & 1]);
-        umma_commit(&sm.v_free[v_stage]);
+        if (leader) {
+          issue_pv(tmem + kColO, tmem + v_stage * 128, v_lo0 + v_stage * kStageLo, 2 * i + 1 < n, i > 0);
+          umma_commit(&sm.o_done[i & 1]);
+          umma_commit(&sm.v_free[v_stage]);
+        }
         if (++v_stage == kStages) {
           v_stage = 0;
           v_phase ^= 1;
