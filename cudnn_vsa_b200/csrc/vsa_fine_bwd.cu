@@ -56,7 +56,7 @@ VSA_DEVICE void store_grad_columns(bool have_acc, uint32_t tmem_addr, float term
 namespace {
 
 constexpr int kGroupThreads = 128;  // one score-math warpgroup
-constexpr int kDkvThreads = 352;    // warps 0..7: two score-math warpgroups, warp 8: MMA issue, warps 9 / 10: TMA loads of K, V, Q / of dO
+constexpr int kDkvThreads = 384;    // warps 0..7: two score-math warpgroups, warp 8: issues the gradient products, warps 9 / 10: TMA loads of K, V, Q / of dO, warp 11: issues the score products
 constexpr int kDkvTmemCols = 512;   // per warpgroup g: S [128g, 128g+64)  dP [128g+64, 128g+128);  dK^T [256,320)  dV^T [320,384)
 constexpr uint32_t kColDk = 256, kColDv = 320;
 constexpr int kPairBytes = 2 * kTileBytes;  // [dim half][tile of the pair][row][128 B]
@@ -69,7 +69,7 @@ struct DkvSmem {  // placed at a 1024-byte aligned address; every tile offset is
   uint8_t pt[2][kTileBytes];   // per warpgroup: P  [128 queries][64 keys] BF16, 128-byte swizzle
   uint8_t dst[2][kTileBytes];  // per warpgroup: dS [128 queries][64 keys]
   long long out_row[kBlock];
-  uint64_t kv_full, q_full[2], do_full[2], q_free[2], do_free[2], sp_done[2], pd_ready[2], pd_free[2], dkv_final;
+  uint64_t kv_full, q_full[2], do_full[2], q_free[2], do_free[2], sp_done[2], sp_free[2], pd_ready[2], pd_free[2], dkv_final;
   uint32_t tmem_base;
   int abort_flag;
 };
@@ -124,10 +124,10 @@ VSA_DEVICE void issue_pair_grad(uint32_t tmem_d, uint32_t a_mn_lo, uint32_t b_lo
 // rows as K.  Query rows sit on the TMEM lanes, so a score-math thread owns one query row and
 // needs one LSE and one delta per pair.  Two warpgroups take alternate pairs, each with its own
 // S / dP accumulators and P / dS buffers.  A pair's Q stage is held until its dK product has
-// read it and its dO stage until the dV product; there is room for two stages of each, so the
-// refill latency is hidden by the issue order  dK(i) dV(i) dK(i+1) dV(i+1) S(i+2) dP(i+2)
-// S(i+3) dP(i+3): every refill has about three products' time to land, and Q and dO have a
-// producer warp each so that neither load queues behind the other's wait.
+// read it and its dO stage until the dV product; there is room for two stages of each.  One
+// warp issues the score products and another the gradient products, synchronised only through
+// mbarriers, so a score product waiting for its refill never holds up a gradient product; Q
+// and dO have a producer warp each so that neither load queues behind the other's wait.
 __global__ void __launch_bounds__(kDkvThreads, 1) fine_bwd_dkv_kernel(const __grid_constant__ FineBwdParams p) {
   extern __shared__ uint8_t smem_raw[];
   DkvSmem& sm = *reinterpret_cast<DkvSmem*>(smem_raw + ((1024 - (smem_u32(smem_raw) & 1023)) & 1023));
@@ -147,6 +147,7 @@ __global__ void __launch_bounds__(kDkvThreads, 1) fine_bwd_dkv_kernel(const __gr
       mbar_init(&sm.q_free[i], 1);
       mbar_init(&sm.do_free[i], 1);
       mbar_init(&sm.sp_done[i], 1);
+      mbar_init(&sm.sp_free[i], kGroupThreads);
       mbar_init(&sm.pd_ready[i], kGroupThreads);
       mbar_init(&sm.pd_free[i], 1);
     }
@@ -202,21 +203,22 @@ __global__ void __launch_bounds__(kDkvThreads, 1) fine_bwd_dkv_kernel(const __gr
         }
       }
     }
-  } else if (warp == 8) {
-    // ------------------------------------------------------------ issuer: MMAs
-    // The whole warp walks the loop (uniform control flow and addresses); one elected lane
-    // issues the MMAs and commits.
+  } else if (warp == 11) {
+    // ------------------------------------------------------------ issuer of the score products
+    // Two issuing warps, one per kind of product, synchronised only through the barriers: the
+    // score products of pair j + 2 start as soon as their stage has been refilled and warpgroup
+    // j & 1 has pulled pair j out of the accumulators; the gradient products never wait for a
+    // refill.  The whole warp walks the loop (uniform control flow and addresses); one elected
+    // lane issues the MMAs and commits.
     if (n > 0) {
       const bool leader = elect_one();
       const uint32_t k_lo = umma_desc_lo(smem_u32(sm.k), 16), v_lo = umma_desc_lo(smem_u32(sm.v), 16);
       const uint32_t q_lo0 = umma_desc_lo(smem_u32(sm.q[0]), 16), do_lo0 = umma_desc_lo(smem_u32(sm.d_o[0]), 16);
-      const uint32_t q_mn_lo0 = umma_desc_lo(smem_u32(sm.q[0]), kTileBytes);
-      const uint32_t do_mn_lo0 = umma_desc_lo(smem_u32(sm.d_o[0]), kTileBytes);
-      const uint32_t pt_lo0 = umma_desc_lo(smem_u32(sm.pt[0]), kHalfTileBytes);
-      const uint32_t dst_lo0 = umma_desc_lo(smem_u32(sm.dst[0]), kHalfTileBytes);
-      constexpr uint32_t kPairLo = kPairBytes >> 4, kBufLo = kTileBytes >> 4;
-      auto scores = [&](int j) {
+      constexpr uint32_t kPairLo = kPairBytes >> 4;
+      mbar_wait(&sm.kv_full, 0, abort_flag, p.status, 21);
+      for (int j = 0; j < pairs; ++j) {
         const int b = j & 1;
+        if (j >= 2) mbar_wait(&sm.sp_free[b], ((j >> 1) - 1) & 1, abort_flag, p.status, 28);
         mbar_wait(&sm.q_full[b], (j >> 1) & 1, abort_flag, p.status, 26);
         tc_fence_after();
         if (leader) issue_pair_scores(tmem + b * 128, q_lo0 + b * kPairLo, k_lo);
@@ -226,11 +228,19 @@ __global__ void __launch_bounds__(kDkvThreads, 1) fine_bwd_dkv_kernel(const __gr
           issue_pair_scores(tmem + b * 128 + 64, do_lo0 + b * kPairLo, v_lo);
           umma_commit(&sm.sp_done[b]);
         }
-      };
-      auto grads = [&](int j) {
+      }
+    }
+  } else if (warp == 8) {
+    // ------------------------------------------------------------ issuer of the gradient products
+    if (n > 0) {
+      const bool leader = elect_one();
+      const uint32_t q_mn_lo0 = umma_desc_lo(smem_u32(sm.q[0]), kTileBytes);
+      const uint32_t do_mn_lo0 = umma_desc_lo(smem_u32(sm.d_o[0]), kTileBytes);
+      const uint32_t pt_lo0 = umma_desc_lo(smem_u32(sm.pt[0]), kHalfTileBytes);
+      const uint32_t dst_lo0 = umma_desc_lo(smem_u32(sm.dst[0]), kHalfTileBytes);
+      constexpr uint32_t kPairLo = kPairBytes >> 4, kBufLo = kTileBytes >> 4;
+      for (int j = 0; j < pairs; ++j) {
         const int b = j & 1;
-        // P and dS of pair j are in shared memory, so its warpgroup has also finished reading
-        // its S / dP accumulators.
         mbar_wait(&sm.pd_ready[b], (j >> 1) & 1, abort_flag, p.status, 29);
         tc_fence_after();
         const bool two = 2 * j + 1 < n;
@@ -241,15 +251,6 @@ __global__ void __launch_bounds__(kDkvThreads, 1) fine_bwd_dkv_kernel(const __gr
           umma_commit(&sm.do_free[b]);
           umma_commit(&sm.pd_free[b]);
         }
-      };
-      mbar_wait(&sm.kv_full, 0, abort_flag, p.status, 21);
-      scores(0);
-      if (pairs > 1) scores(1);
-      for (int i = 0; i < pairs; i += 2) {
-        grads(i);
-        if (i + 1 < pairs) grads(i + 1);
-        if (i + 2 < pairs) scores(i + 2);
-        if (i + 3 < pairs) scores(i + 3);
       }
       if (leader) umma_commit(&sm.dkv_final);
     }
@@ -295,6 +296,11 @@ __global__ void __launch_bounds__(kDkvThreads, 1) fine_bwd_dkv_kernel(const __gr
         VSA_TMEM_LD_32x32b_X32(s_bits, tmem_s + c * 32);
         VSA_TMEM_LD_32x32b_X32(dp_bits, tmem_s + 64 + c * 32);
         tmem_wait_ld();
+        if (c == 1) {
+          // Both halves of S and dP are in registers: the accumulators may be overwritten.
+          tc_fence_before();
+          mbar_arrive(&sm.sp_free[group]);
+        }
         uint32_t p_packed[16], ds_packed[16];
 #pragma unroll
         for (int e = 0; e < 32; e += 2) {

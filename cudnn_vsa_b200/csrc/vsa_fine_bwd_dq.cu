@@ -11,8 +11,9 @@
 // LSE (natural log), dS^T = P^T * (dP^T - delta) * scale is written as BF16 rows [key][query],
 // which is directly the MN-major B operand of the third product; K^T is the K pair read MN-major.
 // Two warpgroups take alternate pairs, each with its own S^T / dP^T accumulators and dS^T buffer,
-// and one thread issues every MMA in the fixed order  ... dQ(i)  S,dP(i+2)  dQ(i+1)  S,dP(i+3) ...
-// so the exponentials of one pair run under the products of its neighbours.  K pair stages are
+// one warp issues the score products and another the dQ products, synchronised only through
+// mbarriers, so the exponentials of one pair run under the products of its neighbours and a wait
+// of one kind of product never holds up the other.  K pair stages are
 // held until their dQ product has read them (three stages), V pair stages only until dP^T (two).
 // The epilogue adds the gradient that reaches a row through its block's pooled mean and scatters
 // the rows to the caller's row order, skipping padding slots (reference vsa_core.py:23-30, 42-47;
@@ -27,7 +28,7 @@ namespace {
 
 constexpr int kGroupThreads = 128;  // one score-math warpgroup
 constexpr int kMathThreads = 256;   // warps 0..3: warpgroup 0 (even pairs), warps 4..7: warpgroup 1 (odd pairs)
-constexpr int kThreads = 352;       // warp 8: tcgen05.mma issue, warps 9 / 10: TMA loads of Q, dO, K / of V
+constexpr int kThreads = 384;       // warp 8: issues the dQ products, warps 9 / 10: TMA loads of Q, dO, K / of V, warp 11: issues the score products
 constexpr int kTmemCols = 512;      // per warpgroup g: S^T [128g, 128g+64)  dP^T [128g+64, 128g+128);  dQ^T [256,320)
 constexpr uint32_t kColDq = 256;
 constexpr int kKStages = 3;
@@ -44,7 +45,7 @@ struct DqSmem {  // placed at a 1024-byte aligned address; every tile offset is 
   float delta[kBlock];
   long long out_row[kBlock];
   uint64_t qdo_full, k_full[kKStages], v_full[kVStages], k_free[kKStages], v_free[kVStages];
-  uint64_t sp_done[2], ds_ready[2], ds_free[2], dq_final;
+  uint64_t sp_done[2], sp_free[2], ds_ready[2], ds_free[2], dq_final;
   uint32_t tmem_base;
   int abort_flag;
 };
@@ -96,6 +97,7 @@ __global__ void __launch_bounds__(kThreads, 1) fine_bwd_dq_kernel(const __grid_c
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(&sm.sp_done[i], 1);
+      mbar_init(&sm.sp_free[i], kGroupThreads);
       mbar_init(&sm.ds_ready[i], kGroupThreads);
       mbar_init(&sm.ds_free[i], 1);
     }
@@ -158,8 +160,11 @@ __global__ void __launch_bounds__(kThreads, 1) fine_bwd_dq_kernel(const __grid_c
         }
       }
     }
-  } else if (warp == 8) {
-    // ------------------------------------------------------------ issuer: MMAs
+  } else if (warp == 11) {
+    // ------------------------------------------------------------ issuer of the score products
+    // Two issuing warps, one per kind of product, synchronised only through the barriers: the
+    // score products of pair j + 2 start as soon as their operands have landed and warpgroup
+    // j & 1 has pulled pair j out of the accumulators, whatever the dQ products are waiting for.
     // The whole warp walks the loop (uniform control flow and addresses); one elected lane
     // issues the MMAs and commits.
     if (n > 0) {
@@ -167,18 +172,19 @@ __global__ void __launch_bounds__(kThreads, 1) fine_bwd_dq_kernel(const __grid_c
       const uint32_t q_lo = umma_desc_lo(smem_u32(sm.q), 16);
       const uint32_t do_lo = umma_desc_lo(smem_u32(sm.d_o), 16);
       const uint32_t k_lo0 = umma_desc_lo(smem_u32(sm.k[0]), 16);
-      const uint32_t k_mn_lo0 = umma_desc_lo(smem_u32(sm.k[0]), kTileBytes);
       const uint32_t v_lo0 = umma_desc_lo(smem_u32(sm.v[0]), 16);
-      const uint32_t ds_lo0 = umma_desc_lo(smem_u32(sm.ds[0]), kHalfTileBytes);
-      constexpr uint32_t kPairLo = kPairBytes >> 4, kDsLo = kTileBytes >> 4;
-      int s_k = 0, s_v = 0, d_k = 0;              // stages of the next score products / the next dQ product
-      uint32_t s_k_phase = 0, s_v_phase = 0;      // parities of those stages' current fills
-      auto scores = [&](int j) {
+      constexpr uint32_t kPairLo = kPairBytes >> 4;
+      int s_k = 0, s_v = 0;                   // stages of the next score products
+      uint32_t s_k_phase = 0, s_v_phase = 0;  // parities of those stages' current fills
+      mbar_wait(&sm.qdo_full, 0, abort_flag, p.status, 11);
+      for (int j = 0; j < pairs; ++j) {
+        if (j >= 2) mbar_wait(&sm.sp_free[j & 1], ((j >> 1) - 1) & 1, abort_flag, p.status, 17);
         mbar_wait(&sm.k_full[s_k], s_k_phase, abort_flag, p.status, 15);
+        tc_fence_after();
+        if (leader) issue_scores(tmem + (j & 1) * 128, k_lo0 + s_k * kPairLo, q_lo);
         mbar_wait(&sm.v_full[s_v], s_v_phase, abort_flag, p.status, 15);
         tc_fence_after();
         if (leader) {
-          issue_scores(tmem + (j & 1) * 128, k_lo0 + s_k * kPairLo, q_lo);
           issue_scores(tmem + (j & 1) * 128 + 64, v_lo0 + s_v * kPairLo, do_lo);
           umma_commit(&sm.sp_done[j & 1]);
           umma_commit(&sm.v_free[s_v]);
@@ -191,13 +197,17 @@ __global__ void __launch_bounds__(kThreads, 1) fine_bwd_dq_kernel(const __grid_c
           s_v = 0;
           s_v_phase ^= 1;
         }
-      };
-      mbar_wait(&sm.qdo_full, 0, abort_flag, p.status, 11);
-      scores(0);
-      if (pairs > 1) scores(1);
+      }
+    }
+  } else if (warp == 8) {
+    // ------------------------------------------------------------ issuer of the dQ products
+    if (n > 0) {
+      const bool leader = elect_one();
+      const uint32_t k_mn_lo0 = umma_desc_lo(smem_u32(sm.k[0]), kTileBytes);
+      const uint32_t ds_lo0 = umma_desc_lo(smem_u32(sm.ds[0]), kHalfTileBytes);
+      constexpr uint32_t kPairLo = kPairBytes >> 4, kDsLo = kTileBytes >> 4;
+      int d_k = 0;  // K stage of the next dQ product
       for (int i = 0; i < pairs; ++i) {
-        // dS^T of pair i is in shared memory, so its warpgroup has also finished reading its
-        // S^T / dP^T accumulators: they may be overwritten by pair i + 2 below.
         mbar_wait(&sm.ds_ready[i & 1], (i >> 1) & 1, abort_flag, p.status, 18);
         tc_fence_after();
         if (leader) {
@@ -206,7 +216,6 @@ __global__ void __launch_bounds__(kThreads, 1) fine_bwd_dq_kernel(const __grid_c
           umma_commit(&sm.ds_free[i & 1]);
         }
         if (++d_k == kKStages) d_k = 0;
-        if (i + 2 < pairs) scores(i + 2);
       }
       if (leader) umma_commit(&sm.dq_final);
     }
@@ -232,6 +241,11 @@ __global__ void __launch_bounds__(kThreads, 1) fine_bwd_dq_kernel(const __grid_c
         VSA_TMEM_LD_32x32b_X32(s_bits, tmem_s + c * 32);
         VSA_TMEM_LD_32x32b_X32(dp_bits, tmem_s + 64 + c * 32);
         tmem_wait_ld();
+        if (c == 1) {
+          // Both halves of S^T and dP^T are in registers: the accumulators may be overwritten.
+          tc_fence_before();
+          mbar_arrive(&sm.sp_free[group]);
+        }
 #pragma unroll
         for (int e = 0; e < 32; e += 4) {
           const float4 nl = *reinterpret_cast<const float4*>(&sm.neg_lse2[c * 32 + e]);
