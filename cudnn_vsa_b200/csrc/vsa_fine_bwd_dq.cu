@@ -225,13 +225,19 @@ __global__ void __launch_bounds__(kThreads, 1) fine_bwd_dq_kernel(const __grid_c
     uint8_t* ds_row = sm.ds[group] + key * 128;
     const int tile = key >> 6, key_in_block = key & 63;
     const float scale = p.scale, sl2 = p.scale * kLog2eBwd;
-    // The valid length of a block comes from two dependent global loads (list, then sizes); they
-    // are issued one round ahead so their latency never sits in the loop.
+    // The valid length of a block comes from two dependent global loads (list, then sizes).  They
+    // are software-pipelined over two rounds - the block id is fetched two rounds ahead, the size
+    // one round ahead from an id that is already in a register - so no load is issued behind the
+    // one it depends on.
     int size_next = kBlock;
     if (p.kv_sizes != nullptr && 2 * group + tile < n) size_next = p.kv_sizes[list[2 * group + tile]];
+    int block_next = (p.kv_sizes != nullptr && 2 * group + 4 + tile < n) ? list[2 * group + 4 + tile] : 0;
     for (int i = group; i < pairs; i += 2) {
       const bool live = (2 * i + tile < n) && key_in_block < size_next;
-      if (p.kv_sizes != nullptr && 2 * i + 4 + tile < n) size_next = p.kv_sizes[list[2 * i + 4 + tile]];
+      if (p.kv_sizes != nullptr) {
+        if (2 * i + 4 + tile < n) size_next = p.kv_sizes[block_next];
+        if (2 * i + 8 + tile < n) block_next = list[2 * i + 8 + tile];
+      }
       mbar_wait(&sm.sp_done[group], (i >> 1) & 1, abort_flag, p.status, 13);
       tc_fence_after();
       uint32_t packed[32];

@@ -11,10 +11,9 @@
 // 128-row K-major operand ([dim half][tile][row][128 B], four 8 KiB TMA boxes); V tiles stay
 // separate and are read MN-major.
 //
-// S has three buffers in tensor memory (S0 S1 S2 O, 4 x 128 columns, one CTA per SM) and a single
-// thread issues every MMA in the fixed order  ... P V(i)  Q K(i+3)  P V(i+1)  Q K(i+4) ...  so
-// the softmax of the next pairs runs under the products of their neighbours and neither side
-// waits for a hand-off.  What bounds a pair outside
+// S has three buffers in tensor memory (S0 S1 S2 O, 4 x 128 columns, one CTA per SM); one warp
+// issues the S products and another the P V products, synchronised only through mbarriers, so
+// the softmax of the next pairs runs under the products of their neighbours.  What bounds a pair outside
 // the tensor core is the exponential unit (16 per clock per SM: 512 cycles for the 8192 scores
 // of a pair), so all 256 softmax threads work on every pair - four threads per query row, 32
 // scores each; the two warpgroups exchange the row maxima through shared memory - instead of
@@ -36,7 +35,7 @@ namespace vsa {
 namespace {
 
 constexpr int kSoftmaxThreads = 256;  // warps 0..7: softmax and epilogue (four threads per query row)
-constexpr int kThreads = 352;         // warp 8: tcgen05.mma issue, warp 9: TMA loads of Q and K, warp 10: of V
+constexpr int kThreads = 384;         // warp 8: issues the P V products, warp 9: TMA loads of Q and K, warp 10: of V, warp 11: issues the S products
 constexpr int kTmemCols = 512;        // S / P buffers b = 0..2 at [128 b, 128 b + 128)   O [384,512)
 constexpr int kSBuffers = 3;
 constexpr uint32_t kColO = 384;
@@ -51,7 +50,7 @@ struct FwdSmem {  // placed at a 1024-byte aligned address; every tile offset is
   float m_part[2][2][kBlock];          // [pair parity][warpgroup][query row]: maximum over the warpgroup's columns
   float l_part[2][kBlock];             // [warpgroup][query row]: partial softmax denominators (epilogue)
   uint64_t q_full, k_full[kStages], v_full[kStages], k_free[kStages], v_free[kStages];
-  uint64_t s_done[kSBuffers], p_ready[kSBuffers], o_done[2];
+  uint64_t s_done[kSBuffers], p_ready[kSBuffers], p_free[kSBuffers], o_done[2];
   uint32_t tmem_base;
   int abort_flag;
 };
@@ -113,6 +112,7 @@ __global__ void __launch_bounds__(kThreads, 1) fine_fwd_kernel(const __grid_cons
     for (int i = 0; i < kSBuffers; ++i) {
       mbar_init(&sm.s_done[i], 1);
       mbar_init(&sm.p_ready[i], kSoftmaxThreads);
+      mbar_init(&sm.p_free[i], 1);
     }
     mbar_init(&sm.o_done[0], 1);
     mbar_init(&sm.o_done[1], 1);
@@ -174,67 +174,79 @@ __global__ void __launch_bounds__(kThreads, 1) fine_fwd_kernel(const __grid_cons
         for (int t = 0; t < count; ++t) tma_load_tile(sm.v[stage][t], &p.v_map, &sm.v_full[stage], head, list[2 * i + t]);
       }
     }
-  } else if (warp == 8) {
-    // ------------------------------------------------------------ issuer: MMAs
-    // The whole warp walks the loop (uniform control flow and addresses); one elected lane
-    // issues the MMAs and commits.
+  } else if (warp == 11) {
+    // ------------------------------------------------------------ issuer of the S products
+    // Two issuing warps, one per kind of product, synchronised only through the barriers, so a
+    // wait of one kind never holds up the other.  The whole warp walks the loop (uniform control
+    // flow and addresses); one elected lane issues the MMAs and commits.
     if (n > 0) {
       const bool leader = elect_one();
-      // Everything the loop needs is in registers: descriptor low words, barrier addresses by
-      // stage, and stage / phase counters that advance without divisions.
       const uint32_t q_lo = umma_desc_lo(smem_u32(sm.q), 16);
       const uint32_t k_lo0 = umma_desc_lo(smem_u32(sm.k[0]), 16);
-      const uint32_t v_lo0 = umma_desc_lo(smem_u32(sm.v[0][0]), kHalfTileBytes);
       constexpr uint32_t kStageLo = (2 * kTileBytes) >> 4;
       static_assert(kStages == kSBuffers, "one counter walks the K stages and the S buffers");
-      int k_stage = 0, v_stage = 0;       // stage (= S buffer) of the next S product / the next P V product
-      uint32_t k_phase = 0, v_phase = 0;  // parity of that stage's current fill (= round of the S buffer)
-      auto qk = [&](int j) {
-        mbar_wait(&sm.k_full[k_stage], k_phase, abort_flag, p.status, 2);
-        tc_fence_after();
-        if (leader) {
-          issue_qk(tmem + k_stage * 128, q_lo, k_lo0 + k_stage * kStageLo, 2 * j + 1 < n);
-          umma_commit(&sm.s_done[k_stage]);
-          umma_commit(&sm.k_free[k_stage]);
-        }
-        if (++k_stage == kStages) {
-          k_stage = 0;
-          k_phase ^= 1;
-        }
-      };
+      int stage = 0;       // K stage = S buffer of the next S product
+      uint32_t phase = 0;  // parity of that stage's current fill
       mbar_wait(&sm.q_full, 0, abort_flag, p.status, 1);
-      for (int j = 0; j < kSBuffers && j < pairs; ++j) qk(j);
-      for (int i = 0; i < pairs; ++i) {
-        mbar_wait(&sm.p_ready[v_stage], v_phase, abort_flag, p.status, 9);
-        mbar_wait(&sm.v_full[v_stage], v_phase, abort_flag, p.status, 6);
+      for (int j = 0; j < pairs; ++j) {
+        // The S product of pair j overwrites P of pair j - 3: its P V product must have read it.
+        if (j >= kSBuffers) mbar_wait(&sm.p_free[stage], phase ^ 1, abort_flag, p.status, 8);
+        mbar_wait(&sm.k_full[stage], phase, abort_flag, p.status, 2);
         tc_fence_after();
         if (leader) {
-          issue_pv(tmem + kColO, tmem + v_stage * 128, v_lo0 + v_stage * kStageLo, 2 * i + 1 < n, i > 0);
+          issue_qk(tmem + stage * 128, q_lo, k_lo0 + stage * kStageLo, 2 * j + 1 < n);
+          umma_commit(&sm.s_done[stage]);
+          umma_commit(&sm.k_free[stage]);
+        }
+        if (++stage == kStages) {
+          stage = 0;
+          phase ^= 1;
+        }
+      }
+    }
+  } else if (warp == 8) {
+    // ------------------------------------------------------------ issuer of the P V products
+    if (n > 0) {
+      const bool leader = elect_one();
+      const uint32_t v_lo0 = umma_desc_lo(smem_u32(sm.v[0][0]), kHalfTileBytes);
+      constexpr uint32_t kStageLo = (2 * kTileBytes) >> 4;
+      int stage = 0;       // V stage = S / P buffer of the next P V product
+      uint32_t phase = 0;  // parity of that stage's current fill
+      for (int i = 0; i < pairs; ++i) {
+        mbar_wait(&sm.p_ready[stage], phase, abort_flag, p.status, 9);
+        mbar_wait(&sm.v_full[stage], phase, abort_flag, p.status, 6);
+        tc_fence_after();
+        if (leader) {
+          issue_pv(tmem + kColO, tmem + stage * 128, v_lo0 + stage * kStageLo, 2 * i + 1 < n, i > 0);
           umma_commit(&sm.o_done[i & 1]);
-          umma_commit(&sm.v_free[v_stage]);
+          umma_commit(&sm.v_free[stage]);
+          umma_commit(&sm.p_free[stage]);
         }
-        if (++v_stage == kStages) {
-          v_stage = 0;
-          v_phase ^= 1;
+        if (++stage == kStages) {
+          stage = 0;
+          phase ^= 1;
         }
-        // The S product of pair i + 3 overwrites P of pair i; MMAs of one thread run in issue
-        // order, so it starts after the P V product above has read its operand.
-        if (i + kSBuffers < pairs) qk(i + kSBuffers);
       }
     }
   } else {
     // ------------------------------------------------------------ softmax warps
     // Thread (row, half, group) owns keys [32 group, 32 group + 32) of KV block `half` of the pair.
-    // The valid length of a tile comes from two dependent global loads (list, then sizes); they
-    // are issued one pair ahead so their latency never sits in the loop.
+    // The valid length of a tile comes from two dependent global loads (list, then sizes).  They
+    // are software-pipelined over two pairs - the block id is fetched two pairs ahead, the size
+    // one pair ahead from an id that is already in a register - so no load is ever issued behind
+    // the one it depends on and their latency never sits in the loop.
     int size_next = kBlock;
     if (p.kv_sizes != nullptr && half < n) size_next = p.kv_sizes[list[half]];
+    int block_next = (p.kv_sizes != nullptr && 2 + half < n) ? list[2 + half] : 0;  // of pair 1
     int buf = 0;           // S buffer of pair i
     uint32_t buf_round = 0;  // parity of that buffer's current use
     for (int i = 0; i < pairs; ++i) {
       const bool present = 2 * i + half < n;  // an odd list ends with half a pair
       const int kv_left = (present ? size_next : 0) - 32 * group;  // valid keys among this thread's 32
-      if (p.kv_sizes != nullptr && 2 * i + 2 + half < n) size_next = p.kv_sizes[list[2 * i + 2 + half]];
+      if (p.kv_sizes != nullptr) {
+        if (2 * i + 2 + half < n) size_next = p.kv_sizes[block_next];
+        if (2 * i + 4 + half < n) block_next = list[2 * i + 4 + half];
+      }
       const uint32_t tmem_s = tmem + lane_base + buf * 128;
       mbar_wait(&sm.s_done[buf], buf_round, abort_flag, p.status, 3);
       tc_fence_after();
