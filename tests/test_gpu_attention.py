@@ -97,7 +97,10 @@ def _random_lists(heads, q_blocks, kv_blocks, cap, gen):
     return index, counts
 
 
-@pytest.mark.parametrize("heads,q_blocks,kv_blocks,cap", [(1, 2, 3, 3), (2, 5, 9, 6), (3, 4, 40, 33)])
+# List lengths from 0 to `cap`: every tail of the pair / stage / buffer rings (odd lists, one pair
+# only, lengths around the ring wrap points) occurs in some (head, query block).
+@pytest.mark.parametrize("heads,q_blocks,kv_blocks,cap", [(1, 2, 3, 3), (2, 5, 9, 6), (3, 4, 40, 33), (2, 24, 20, 15),
+                                                           (1, 9, 70, 64)])
 def test_fine_forward_and_backward_on_given_lists(heads, q_blocks, kv_blocks, cap):
     gen = torch.Generator().manual_seed(11)
     q = torch.randn(q_blocks * BLOCK, heads, 128, generator=gen).to(torch.bfloat16)
