@@ -358,7 +358,7 @@ def main():
         # DRAM bytes per listed block pair from the ncu captures of the 6-head single sample
         # (profiles/<kernel>_720p_single_sample_h6.md: dram read + write over 2,623,488 pairs),
         # scaled to this workload by its number of listed pairs (traffic grows with the tiles).
-        per_pair = {"fine_fwd_kernel": 1421.2, "fine_bwd_dq_kernel": 1332.5, "fine_bwd_dkv_kernel": 2247.4}
+        per_pair = {"fine_fwd_kernel": 1515.8, "fine_bwd_dq_kernel": 1508.8, "fine_bwd_dkv_kernel": 2225.6}
         listed = float(layout.routing_counts.sum().item())
         traffic = per_pair[name] * listed
         result["roofline"] = {"kernel": name, "bound": "tensor", "achieved": top["achieved"],
