@@ -416,7 +416,7 @@ def main():
             return start.elapsed_time(stop) / steps
         e2e_run(2)
         barrier()
-        e2e_steps = min(args.steps, 5)
+        e2e_steps = min(args.steps, 10)
         e2e_ms = torch.tensor([e2e_run(e2e_steps)], device=device, dtype=torch.float64)
         if world > 1:
             dist.all_reduce(e2e_ms, op=dist.ReduceOp.MAX)
