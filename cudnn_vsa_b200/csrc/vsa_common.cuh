@@ -81,22 +81,9 @@ VSA_DEVICE bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_fl
 VSA_DEVICE void mbar_arrive(uint64_t* bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
-// Named barrier `id` over `threads` threads (a subset of the CTA's warps), and the same with an
-// OR reduction of a per-thread predicate.
+// Named barrier `id` over `threads` threads (a subset of the CTA's warps).
 VSA_DEVICE void named_barrier(int id, int threads) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
-}
-VSA_DEVICE bool named_barrier_or(int id, int threads, bool value) {
-  uint32_t out;
-  asm volatile(
-      "{\n\t.reg .pred p, q;\n\t"
-      "setp.ne.b32 q, %3, 0;\n\t"
-      "bar.red.or.pred p, %1, %2, q;\n\t"
-      "selp.b32 %0, 1, 0, p;\n\t}"
-      : "=r"(out)
-      : "r"(id), "r"(threads), "r"(static_cast<uint32_t>(value))
-      : "memory");
-  return out != 0;
 }
 
 VSA_DEVICE void fence_barrier_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
@@ -155,19 +142,13 @@ VSA_DEVICE void umma_commit(uint64_t* bar) {
                : "memory");
 }
 
-// Shared-memory matrix descriptor, 128-byte swizzle, descriptor version 1 (sm_100).
-//   K-major operand  (rows = M or N, 128 bytes of K per row): lbo unused, sbo = 1024 (8 rows).
-//   MN-major operand (rows = K, 128 bytes of M/N per row): lbo = bytes to the next 64 M/N elements,
-//                     sbo = 1024 (next 8 K rows).
-VSA_DEVICE uint64_t umma_smem_desc(uint32_t smem_addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
-  uint64_t desc = 0;
-  desc |= static_cast<uint64_t>((smem_addr & 0x3FFFF) >> 4);
-  desc |= static_cast<uint64_t>((lbo_bytes >> 4) & 0x3FFF) << 16;
-  desc |= static_cast<uint64_t>((sbo_bytes >> 4) & 0x3FFF) << 32;
-  desc |= static_cast<uint64_t>(1) << 46;  // version
-  desc |= static_cast<uint64_t>(2) << 61;  // SWIZZLE_128B
-  return desc;
-}
+// Shared-memory matrix descriptor, 128-byte swizzle, descriptor version 1 (sm_100): 64 bits with
+// the start address / 16 in bits 0-13, LBO / 16 in bits 16-29, SBO / 16 in bits 32-45, the version
+// in bit 46 and the swizzle mode (2 = 128 bytes) in bits 61-63.
+//   K-major operand  (rows = M or N, 128 bytes of K per row): LBO unused, SBO = 1024 (8 rows).
+//   MN-major operand (rows = K, 128 bytes of M/N per row): LBO = bytes to the next 64 M/N elements,
+//                     SBO = 1024 (next 8 K rows).
+// The kernels carry a descriptor as its low word (umma_desc_lo below); the high word is constant.
 
 // Instruction descriptor: BF16 x BF16 -> FP32, dense, M x N, operand majors (0 = K, 1 = MN).
 __host__ __device__ constexpr uint32_t umma_idesc(int m, int n, int a_mn_major, int b_mn_major) {
@@ -175,26 +156,6 @@ __host__ __device__ constexpr uint32_t umma_idesc(int m, int n, int a_mn_major, 
          | (1u << 7) | (1u << 10)                // A, B = BF16
          | (static_cast<uint32_t>(a_mn_major) << 15) | (static_cast<uint32_t>(b_mn_major) << 16)
          | (static_cast<uint32_t>(n >> 3) << 17) | (static_cast<uint32_t>(m >> 4) << 24);
-}
-
-// D[tmem] (+)= A[smem] * B[smem]; one K=16 step.  Issued by a single thread.
-VSA_DEVICE void umma_ss(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-      ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
-
-// Same product with the A operand in tensor memory: an M x 16 BF16 slice stored like an
-// accumulator of the same M, two BF16 per 32-bit column (8 columns per K=16 step).
-VSA_DEVICE void umma_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
-      ::"r"(tmem_d), "r"(tmem_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
-      : "memory");
 }
 
 // True in exactly one lane of a converged warp.  Code that the whole warp runs with uniform
@@ -210,12 +171,15 @@ VSA_DEVICE bool elect_one() {
   return pred != 0;
 }
 
-// Lean issue path.  The thread that issues the MMAs is alone in its warp, so every scalar
-// instruction between two MMAs costs its full latency: building two 64-bit descriptors per MMA
-// (about twenty dependent instructions) takes longer than the 64 cycles an M64/N128 MMA runs
-// for, and the tensor pipe starves.  Here a descriptor is carried as its low word only (address
-// and LBO fields; the operand advances by adding bytes/16), the high word is the constant shared
-// by every 128-byte-swizzle operand with SBO = 1024, and the pair is assembled inside the asm.
+// Issue path.  The warp that issues the MMAs has one active lane, so every scalar instruction
+// between two MMAs costs its full latency: building two 64-bit descriptors per MMA (about
+// twenty dependent instructions) takes longer than the 64 cycles an M64/N128 MMA runs for, and
+// the tensor pipe starves.  A descriptor is therefore carried as its low word only (address and
+// LBO fields; the operand advances by adding bytes/16), the high word is the constant shared by
+// every 128-byte-swizzle operand with SBO = 1024, and the pair is assembled inside the asm.
+// D[tmem] (+)= A * B, one K=16 step: `umma_ss_lo` takes both operands from shared memory,
+// `umma_ts_lo` takes A from tensor memory (an M x 16 BF16 slice stored like an accumulator of
+// the same M, two BF16 per 32-bit column, 8 columns per step).
 constexpr uint32_t kDescHi = (1024u >> 4) | (1u << 14) | (2u << 29);  // SBO, version 1, SWIZZLE_128B
 VSA_DEVICE uint32_t umma_desc_lo(uint32_t smem_addr, uint32_t lbo_bytes) {
   return ((smem_addr & 0x3FFFF) >> 4) | ((lbo_bytes >> 4) << 16);
@@ -289,18 +253,6 @@ VSA_DEVICE void umma_ts_lo(uint32_t tmem_d, uint32_t tmem_a, uint32_t b_lo, uint
         "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]),      \
         "=r"(r[29]), "=r"(r[30]), "=r"(r[31])                                                           \
       : "r"(taddr)                                                                                      \
-      : "memory")
-
-#define VSA_TMEM_ST_32x32b_X32(r, taddr)                                                              \
-  asm volatile(                                                                                       \
-      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "                                                 \
-      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "                      \
-      "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"              \
-      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]),        \
-      "r"(r[7]), "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]),       \
-      "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]),    \
-      "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]),    \
-      "r"(r[31])                                                                                        \
       : "memory")
 
 // Byte offset of the 16-byte chunk `chunk` (0..7) of row `row` inside a 64-row x 128-byte
