@@ -24,6 +24,7 @@ SIGNATURES = {
     "vsa_route_scratch_bytes": (_I64, [_I64, _I64, _I32]),
     "vsa_route": (_I32, [_P, _P, _I32, _I32, _I32, _I32, _I32, _I32, _I32, _I32, _I32, _P, _I64, _I32, _P,
                          _I64, _P]),
+    "vsa_selftest_wait_timeout": (_I32, [_P, _I64, _P]),
     "vsa_route_static": (_I32, [_P, _P, _I32, _I32, _I32, _I32, _I32, _I32, _I32, _I32, _I32, _P, _I64, _I32, _P]),
     "vsa_fine_fwd": (_I32, [_P, _P, _P, _I64, _I64, _I32, _P, _P, _I64, _I64, _I32, _P, _F, _P, _P, _P, _P,
                             _P, _P, _P, _I64, _P, _P]),

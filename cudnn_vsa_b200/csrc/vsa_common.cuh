@@ -61,20 +61,24 @@ constexpr long long kWaitCycles = 2000000000LL;
 // every later wait on an incomplete barrier returns at once, so the CTA drains its loops, frees
 // TMEM and exits.  A completed barrier costs one try_wait: the waits of the MMA-issuing thread
 // sit on the critical path of the tensor pipe.
-VSA_DEVICE bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* status,
-                          int site) {
+VSA_DEVICE bool mbar_wait_limit(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* status,
+                                int site, long long limit_cycles) {
   if (mbar_try_wait(bar, parity)) return true;
   if (*abort_flag) return false;
   const long long start = clock64();
   while (!mbar_try_wait(bar, parity)) {
     if (*abort_flag) return false;
-    if (clock64() - start > kWaitCycles) {
+    if (clock64() - start > limit_cycles) {
       *abort_flag = 1;
       if (status != nullptr) atomicCAS(status, 0, kDevWaitTimeout + site);
       return false;
     }
   }
   return true;
+}
+VSA_DEVICE bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* status,
+                          int site) {
+  return mbar_wait_limit(bar, parity, abort_flag, status, site, kWaitCycles);
 }
 
 // One arrival (release) on an mbarrier whose expected count is the number of arriving threads.

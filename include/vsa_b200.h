@@ -84,6 +84,13 @@ int vsa_route_static(const float* q_mean, const float* k_mean, int32_t heads, in
                      int32_t q_mean_offset, int32_t kv_first, int32_t kv_last, int32_t k_mean_offset, int32_t keep,
                      int32_t cursor, int32_t* indices, int64_t index_head_stride, int32_t capacity, void* stream);
 
+/* Self-test of the bounded waits (no counterpart in the reference): launches one small CTA whose
+ * thread 0 waits on an mbarrier that nothing completes, for at most `limit_cycles` SM clocks
+ * (1 .. the library's own limit of about one second).  The kernel gives up, writes 177 (100 +
+ * the self-test's wait site) to *status if it was 0, and returns; later launches work as usual.
+ * Tests use it to check that an expired wait is reported and leaves the context usable. */
+int vsa_selftest_wait_timeout(int32_t* status, int64_t limit_cycles, void* stream);
+
 /* Block-sparse attention forward over 64-slot blocks (tcgen05 + TMA).
  *   q [q_blocks*64, heads, 128], k / v [kv_blocks*64, heads, 128] BF16 slot tensors;
  *   indices [heads, q_blocks, capacity] (head stride 0 = one table for all heads), counts alike;

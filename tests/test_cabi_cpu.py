@@ -76,3 +76,14 @@ def test_reorder_validation_order():
         raster_to_block_wo_padding(x.to(torch.complex64), vsa_layout=block)
     with pytest.raises(ValueError, match="CUDA"):
         block_wo_padding_to_raster(x, vsa_layout=block)
+
+
+def test_selftest_entry_rejects_bad_arguments_on_the_host():
+    lib = _cabi.load()
+    # Null status, non-positive limit, limit beyond the library's own one-second bound: all refused
+    # before anything is launched (no GPU is needed for this).
+    assert lib.vsa_selftest_wait_timeout(None, 1000, None) == 1
+    dummy = ctypes.c_int32(0)
+    pointer = ctypes.cast(ctypes.pointer(dummy), ctypes.c_void_p)
+    assert lib.vsa_selftest_wait_timeout(pointer, 0, None) == 1
+    assert lib.vsa_selftest_wait_timeout(pointer, 1 << 40, None) == 1

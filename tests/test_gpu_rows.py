@@ -2,7 +2,7 @@
 import pytest
 import torch
 
-from cudnn_vsa_b200 import vsa_kernels
+from cudnn_vsa_b200 import _cabi, vsa_core, vsa_kernels
 from cudnn_vsa_b200.vsa import block_wo_padding_to_raster, raster_to_block_wo_padding
 from cudnn_vsa_b200.vsa_layout import build_vsa_layout
 from oracle import vsa_oracle
@@ -86,3 +86,23 @@ def test_offsets_beyond_int32():
     y = vsa_kernels.reorder_tokens(x, perm)
     assert torch.equal(y[:, 0], x[perm, 0]) and torch.equal(y[-1], x[perm[-1]])
     assert torch.equal(vsa_kernels.reorder_tokens(y, perm, inverse=True)[:, -1], x[:, -1])
+
+
+def test_expired_wait_is_reported_and_the_context_stays_usable():
+    # Every mbarrier wait in the tcgen05 kernels is bounded; the self-test entry point makes one
+    # run out (a barrier that nothing completes, two million clocks: about a millisecond).
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    _cabi.call("vsa_selftest_wait_timeout", _cabi.ptr(status), 2_000_000, _cabi.stream())
+    torch.cuda.synchronize()
+    assert int(status.item()) == 177  # 100 + the self-test's wait site
+    # The host side turns a recorded code into an error ...
+    layout = build_vsa_layout(GEOMETRIES["ragged"], head_num=2, device="cuda")
+    plan = vsa_core.device_plan(layout)
+    plan.status.copy_(status)
+    with pytest.raises(RuntimeError, match="177"):
+        vsa_core.check_status(layout)
+    plan.status.zero_()
+    # ... and the context is alive: the next kernels run and give the right answer.
+    x = _values((50, 3), torch.int32)
+    row_map = torch.randint(-1, 50, (77,), device="cuda")
+    assert torch.equal(vsa_kernels.gather(x, row_map).cpu(), vsa_oracle.gather_rows(x.cpu(), row_map.cpu()))
