@@ -49,6 +49,10 @@ struct FwdSmem {  // placed at a 1024-byte aligned address; every tile offset is
   uint8_t v[kStages][2][kTileBytes];   // [tile of the pair][dim half][row][128 B]
   float m_part[2][2][kBlock];          // [pair parity][warpgroup][query row]: maximum over the warpgroup's columns
   float l_part[2][kBlock];             // [warpgroup][query row]: partial softmax denominators (epilogue)
+  // Valid keys of the two KV blocks of a pair (0 = block absent), pair i in slot i % (2 kStages):
+  // a slot is rewritten for pair i + 2 kStages only after the S product of pair i + kStages has
+  // completed, which needs the P V product - hence the softmax - of pair i.
+  int kv_size[2 * kStages][2];
   uint64_t q_full, k_full[kStages], v_full[kStages], k_free[kStages], v_free[kStages];
   uint64_t s_done[kSBuffers], p_ready[kSBuffers], p_free[kSBuffers], o_done[2];
   uint32_t tmem_base;
@@ -154,12 +158,23 @@ __global__ void __launch_bounds__(kThreads, 1) fine_fwd_kernel(const __grid_cons
         const int count = (2 * i + 1 < n) ? 2 : 1;
         const int stage = i % kStages;
         const uint32_t reuse = ((i / kStages) - 1) & 1;  // phase of the release by pair i - kStages
+        // The valid length of each block travels with the stage: the softmax threads read it from
+        // shared memory after the S product of the stage has completed, instead of chasing
+        // list -> sizes through global memory themselves (those loads, queued behind the TMA
+        // traffic, cost the softmax loop a tenth of its time).
+        const int block0 = list[2 * i], block1 = count == 2 ? list[2 * i + 1] : 0;
+        const int size0 = p.kv_sizes != nullptr ? p.kv_sizes[block0] : kBlock;
+        const int size1 = count == 2 ? (p.kv_sizes != nullptr ? p.kv_sizes[block1] : kBlock) : 0;
         if (i >= kStages) mbar_wait(&sm.k_free[stage], reuse, abort_flag, p.status, 3);
+        sm.kv_size[i % (2 * kStages)][0] = size0;
+        sm.kv_size[i % (2 * kStages)][1] = size1;
         mbar_expect_tx(&sm.k_full[stage], count * kTileBytes);
-        for (int t = 0; t < count; ++t)
-          for (int h = 0; h < 2; ++h)
-            tma_load_half(sm.k[stage] + h * kTileBytes + t * kHalfTileBytes, &p.k_half_map, &sm.k_full[stage], head,
-                          list[2 * i + t], h);
+        tma_load_half(sm.k[stage], &p.k_half_map, &sm.k_full[stage], head, block0, 0);
+        tma_load_half(sm.k[stage] + kTileBytes, &p.k_half_map, &sm.k_full[stage], head, block0, 1);
+        if (count == 2) {
+          tma_load_half(sm.k[stage] + kHalfTileBytes, &p.k_half_map, &sm.k_full[stage], head, block1, 0);
+          tma_load_half(sm.k[stage] + kTileBytes + kHalfTileBytes, &p.k_half_map, &sm.k_full[stage], head, block1, 1);
+        }
       }
     }
   } else if (warp == 10) {
@@ -231,25 +246,15 @@ __global__ void __launch_bounds__(kThreads, 1) fine_fwd_kernel(const __grid_cons
   } else {
     // ------------------------------------------------------------ softmax warps
     // Thread (row, half, group) owns keys [32 group, 32 group + 32) of KV block `half` of the pair.
-    // The valid length of a tile comes from two dependent global loads (list, then sizes).  They
-    // are software-pipelined over two pairs - the block id is fetched two pairs ahead, the size
-    // one pair ahead from an id that is already in a register - so no load is ever issued behind
-    // the one it depends on and their latency never sits in the loop.
-    int size_next = kBlock;
-    if (p.kv_sizes != nullptr && half < n) size_next = p.kv_sizes[list[half]];
-    int block_next = (p.kv_sizes != nullptr && 2 + half < n) ? list[2 + half] : 0;  // of pair 1
     int buf = 0;           // S buffer of pair i
     uint32_t buf_round = 0;  // parity of that buffer's current use
     for (int i = 0; i < pairs; ++i) {
-      const bool present = 2 * i + half < n;  // an odd list ends with half a pair
-      const int kv_left = (present ? size_next : 0) - 32 * group;  // valid keys among this thread's 32
-      if (p.kv_sizes != nullptr) {
-        if (2 * i + 2 + half < n) size_next = p.kv_sizes[block_next];
-        if (2 * i + 4 + half < n) block_next = list[2 * i + 4 + half];
-      }
       const uint32_t tmem_s = tmem + lane_base + buf * 128;
       mbar_wait(&sm.s_done[buf], buf_round, abort_flag, p.status, 3);
       tc_fence_after();
+      // Valid keys among this thread's 32 (the K producer wrote the block sizes with the stage;
+      // an odd list ends with half a pair, whose absent block has size 0).
+      const int kv_left = sm.kv_size[i % (2 * kStages)][half] - 32 * group;
       uint32_t s_bits[32];
       VSA_TMEM_LD_16x32bx2_X32(s_bits, tmem_s + 32 * group, 64);
       tmem_wait_ld();
@@ -295,16 +300,21 @@ __global__ void __launch_bounds__(kThreads, 1) fine_fwd_kernel(const __grid_cons
         VSA_TMEM_ST_16x32bx2_X32(o_bits, addr, 64);
       }
       const float m_use = (m_ref == -INFINITY) ? 0.f : m_ref * sl2;
+      const f32x2 sl2_2 = pack_f32x2(sl2, sl2), shift_2 = pack_f32x2(-m_use, -m_use);
       uint32_t packed[16];
-      float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+      f32x2 sum2[4] = {pack_f32x2(0.f, 0.f), pack_f32x2(0.f, 0.f), pack_f32x2(0.f, 0.f), pack_f32x2(0.f, 0.f)};
 #pragma unroll
       for (int e = 0; e < 32; e += 2) {
-        const float p0 = fast_exp2(fmaf(s[e], sl2, -m_use));
-        const float p1 = fast_exp2(fmaf(s[e + 1], sl2, -m_use));
+        float p0, p1;
+        unpack_f32x2(fma_f32x2(pack_f32x2(s[e], s[e + 1]), sl2_2, shift_2), p0, p1);
+        p0 = fast_exp2(p0);
+        p1 = fast_exp2(p1);
         packed[e >> 1] = pack_bf16(p0, p1);
-        sum4[(e >> 1) & 3] += p0 + p1;
+        sum2[(e >> 1) & 3] = add_f32x2(sum2[(e >> 1) & 3], pack_f32x2(p0, p1));
       }
-      l = l * alpha + ((sum4[0] + sum4[1]) + (sum4[2] + sum4[3]));
+      float lo, hi;
+      unpack_f32x2(add_f32x2(add_f32x2(sum2[0], sum2[1]), add_f32x2(sum2[2], sum2[3])), lo, hi);
+      l = l * alpha + (lo + hi);
       // P over the first 64 columns of S, two keys per column: block `half` of the pair in
       // columns [32 half, 32 half + 32), this thread's keys in the 16 columns from 16 group.
       VSA_TMEM_ST_16x32bx2_X16(packed, tmem_s + 16 * group, 32);
