@@ -101,7 +101,9 @@ def bits(t):
 
 
 def main():
-    reference = Path(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) < 2:
+        raise SystemExit("usage: python tests/golden/make_golden.py <path to a checkout of the reference>")
+    reference = Path(sys.argv[1])
     install_stubs(reference)
     import vsa_kernels
     import vsa_layout
