@@ -28,6 +28,7 @@ SIGNATURES = {
     "vsa_route_static": (_I32, [_P, _P, _I32, _I32, _I32, _I32, _I32, _I32, _I32, _I32, _I32, _P, _I64, _I32, _P]),
     "vsa_fine_fwd": (_I32, [_P, _P, _P, _I64, _I64, _I32, _P, _P, _I64, _I64, _I32, _P, _F, _P, _P, _P, _P,
                             _P, _P, _P, _I64, _P, _P]),
+    "vsa_fine_fwd_running": (_I32, [_P, _P, _P, _I64, _I64, _I32, _P, _P, _I64, _I64, _I32, _P, _F, _P, _P, _P, _P]),
     "vsa_merge_bwd": (_I32, [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I64, _I64, _I32, _P]),
     "vsa_kv_mask_words": (_I64, [_I64]),
     "vsa_fine_bwd": (_I32, [_P, _P, _P, _P, _I64, _I64, _I32, _P, _P, _I64, _I64, _I32, _P, _P, _F, _P, _P,
@@ -47,6 +48,54 @@ _lib = None
 
 # Kernels launched by this process through `call` (the benchmark reports the count per step).
 LAUNCHES = 0
+
+# Per-entry-point device timing, off by default: while a `trace()` block is active every `call`
+# is bracketed by two CUDA events on the current stream (`mark` brackets host-side regions such
+# as a stream join the same way).
+_TRACE = None
+
+
+class trace:
+    """``with _cabi.trace() as t: step()`` then ``t.summary()`` gives milliseconds and call counts
+    per entry point, measured on the device between events recorded around each call."""
+
+    def __enter__(self):
+        global _TRACE
+        self.records, self._outer = [], _TRACE
+        _TRACE = self
+        return self
+
+    def __exit__(self, *exc):
+        global _TRACE
+        _TRACE = self._outer
+
+    def summary(self):
+        torch.cuda.synchronize()
+        out = {}
+        for name, start, stop in self.records:
+            entry = out.setdefault(name, {"ms": 0.0, "calls": 0})
+            entry["ms"] += start.elapsed_time(stop)
+            entry["calls"] += 1
+        return out
+
+
+class mark:
+    """Brackets a region of the current stream under ``name`` when a trace is active."""
+
+    def __init__(self, name):
+        self.name = name
+
+    def __enter__(self):
+        self.start = None
+        if _TRACE is not None:
+            self.start = torch.cuda.Event(enable_timing=True)
+            self.start.record()
+
+    def __exit__(self, *exc):
+        if self.start is not None and _TRACE is not None:
+            stop = torch.cuda.Event(enable_timing=True)
+            stop.record()
+            _TRACE.records.append((self.name, self.start, stop))
 
 
 def load():
@@ -80,7 +129,11 @@ def call(name, *args, launches=1):
     ``launches`` is the number of kernels the call enqueues (one for most entry points).
     """
     global LAUNCHES
-    rc = getattr(load(), name)(*args)
+    if _TRACE is not None:
+        with mark(name):
+            rc = getattr(load(), name)(*args)
+    else:
+        rc = getattr(load(), name)(*args)
     LAUNCHES += launches
     if rc != 0:
         detail = _STATUS.get(rc, "unknown status")

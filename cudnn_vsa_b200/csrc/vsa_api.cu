@@ -122,18 +122,26 @@ int vsa_route(const float* q_mean, const float* k_mean, int32_t heads, int32_t q
   return vsa::kOk;
 }
 
-int vsa_fine_fwd(const void* q, const void* k, const void* v, int64_t q_blocks, int64_t kv_blocks, int32_t heads,
-                 const int32_t* indices, const int32_t* counts, int64_t index_head_stride, int64_t count_head_stride,
-                 int32_t capacity, const int32_t* kv_sizes, float scale, void* o_slots, float* lse,
-                 const int64_t* slot_row, const int32_t* block_coarse, const void* gate, const void* coarse,
-                 void* out, int64_t out_rows, int32_t* status, void* stream) {
+}  // extern "C" (reopened below)
+
+namespace {
+
+// Shared by the two forward entry points: checks, tensor maps, launch.
+int fine_fwd_common(const void* q, const void* k, const void* v, int64_t q_blocks, int64_t kv_blocks, int32_t heads,
+                    const int32_t* indices, const int32_t* counts, int64_t index_head_stride,
+                    int64_t count_head_stride, int32_t capacity, const int32_t* kv_sizes, float scale, void* o_slots,
+                    float* lse, float* o_running, const int64_t* slot_row, const int32_t* block_coarse,
+                    const void* gate, const void* coarse, void* out, int64_t out_rows, int32_t* status,
+                    void* stream) {
   if (q == nullptr || k == nullptr || v == nullptr || indices == nullptr || counts == nullptr ||
-      o_slots == nullptr || lse == nullptr || q_blocks < 0 || kv_blocks <= 0 || heads <= 0 || capacity <= 0)
+      (o_slots == nullptr && o_running == nullptr) || lse == nullptr || q_blocks < 0 || kv_blocks <= 0 ||
+      heads <= 0 || capacity <= 0)
     return vsa::kBadArgument;
   if (q_blocks == 0) return vsa::kOk;
   if (q_blocks > 0x7fffffffLL / vsa::kBlock || kv_blocks > 0x7fffffffLL / vsa::kBlock || heads > 65535)
     return vsa::kTooLarge;
   if (block_coarse != nullptr && out != nullptr && (gate == nullptr || coarse == nullptr)) return vsa::kBadArgument;
+  if ((reinterpret_cast<uintptr_t>(o_running) & 15) != 0) return vsa::kBadArgument;
   vsa::FineFwdParams p{};
   int rc = make_tile_map(&p.q_map, q, q_blocks * vsa::kBlock, heads);
   if (rc == vsa::kOk) rc = make_tile_map(&p.k_map, k, kv_blocks * vsa::kBlock, heads);
@@ -148,6 +156,7 @@ int vsa_fine_fwd(const void* q, const void* k, const void* v, int64_t q_blocks, 
   p.kv_sizes = kv_sizes;
   p.o_slots = static_cast<__nv_bfloat16*>(o_slots);
   p.lse = lse;
+  p.o_running = o_running;
   p.slot_row = slot_row;
   p.block_coarse = block_coarse;
   p.gate = static_cast<const __nv_bfloat16*>(gate);
@@ -160,6 +169,31 @@ int vsa_fine_fwd(const void* q, const void* k, const void* v, int64_t q_blocks, 
   p.scale = scale;
   p.status = status;
   return from_cuda(vsa::launch_fine_fwd(p, out != nullptr, as_stream(stream)));
+}
+
+}  // namespace
+
+extern "C" {
+
+int vsa_fine_fwd(const void* q, const void* k, const void* v, int64_t q_blocks, int64_t kv_blocks, int32_t heads,
+                 const int32_t* indices, const int32_t* counts, int64_t index_head_stride, int64_t count_head_stride,
+                 int32_t capacity, const int32_t* kv_sizes, float scale, void* o_slots, float* lse,
+                 const int64_t* slot_row, const int32_t* block_coarse, const void* gate, const void* coarse,
+                 void* out, int64_t out_rows, int32_t* status, void* stream) {
+  if (o_slots == nullptr) return vsa::kBadArgument;
+  return fine_fwd_common(q, k, v, q_blocks, kv_blocks, heads, indices, counts, index_head_stride, count_head_stride,
+                         capacity, kv_sizes, scale, o_slots, lse, nullptr, slot_row, block_coarse, gate, coarse, out,
+                         out_rows, status, stream);
+}
+
+int vsa_fine_fwd_running(const void* q, const void* k, const void* v, int64_t q_blocks, int64_t kv_blocks,
+                         int32_t heads, const int32_t* indices, const int32_t* counts, int64_t index_head_stride,
+                         int64_t count_head_stride, int32_t capacity, const int32_t* kv_sizes, float scale,
+                         float* o_running, float* lse_running, int32_t* status, void* stream) {
+  if (o_running == nullptr) return vsa::kBadArgument;
+  return fine_fwd_common(q, k, v, q_blocks, kv_blocks, heads, indices, counts, index_head_stride, count_head_stride,
+                         capacity, kv_sizes, scale, nullptr, lse_running, o_running, nullptr, nullptr, nullptr, nullptr,
+                         nullptr, 0, status, stream);
 }
 
 int vsa_merge_bwd(const void* grad, const void* gate, const void* coarse, const void* o_slots, const int64_t* slot_row,

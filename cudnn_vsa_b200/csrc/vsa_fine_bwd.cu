@@ -222,7 +222,7 @@ __global__ void __launch_bounds__(kDkvThreads, 1) fine_bwd_dkv_kernel(const __gr
         mbar_wait(&sm.q_full[b], (j >> 1) & 1, abort_flag, p.status, 26);
         tc_fence_after();
         if (leader) issue_pair_scores(tmem + b * 128, q_lo0 + b * kPairLo, k_lo);
-        mbar_wait(&sm.do_full[b], (j >> 1) & 1, abort_flag, p.status, 26);
+        mbar_wait(&sm.do_full[b], (j >> 1) & 1, abort_flag, p.status, 30);
         tc_fence_after();
         if (leader) {
           issue_pair_scores(tmem + b * 128 + 64, do_lo0 + b * kPairLo, v_lo);

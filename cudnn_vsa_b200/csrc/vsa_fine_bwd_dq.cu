@@ -182,7 +182,7 @@ __global__ void __launch_bounds__(kThreads, 1) fine_bwd_dq_kernel(const __grid_c
         mbar_wait(&sm.k_full[s_k], s_k_phase, abort_flag, p.status, 15);
         tc_fence_after();
         if (leader) issue_scores(tmem + (j & 1) * 128, k_lo0 + s_k * kPairLo, q_lo);
-        mbar_wait(&sm.v_full[s_v], s_v_phase, abort_flag, p.status, 15);
+        mbar_wait(&sm.v_full[s_v], s_v_phase, abort_flag, p.status, 19);
         tc_fence_after();
         if (leader) {
           issue_scores(tmem + (j & 1) * 128 + 64, v_lo0 + s_v * kPairLo, do_lo);

@@ -26,7 +26,10 @@
 // in slot order, the natural-log LSE and - when a row map is given - the merged result
 // `fine + gate * coarse[block]` straight into the caller's row order, which replaces the
 // reference's separate restore and gate-add passes (reference vsa_core.py:15-20,
-// vsa_kernels.py:191-201, vsa.py:111-117).
+// vsa_kernels.py:191-201, vsa.py:111-117).  In the ring variant the epilogue instead folds this
+// step's partial result into the caller's running FP32 output and LSE (online-softmax merge of
+// two normalised partials, reference vsa_kernels.py:375-397 and vsa_core.py:237-240), so a ring
+// step neither writes a BF16 partial nor needs a separate merge pass.
 #include "vsa_common.cuh"
 #include "vsa_kernels.h"
 
@@ -92,8 +95,13 @@ VSA_DEVICE void issue_pv(uint32_t tmem_o, uint32_t tmem_p, uint32_t v_lo, bool t
 
 }  // namespace
 
-template <bool kMerge>
+// kMode: 0 = fine output and LSE, 1 = also the merged output in the caller's row order,
+// 2 = fold the partial result into the running FP32 output and LSE (ring step).
+enum : int { kModePlain = 0, kModeMerge = 1, kModeRunning = 2 };
+
+template <int kMode>
 __global__ void __launch_bounds__(kThreads, 1) fine_fwd_kernel(const __grid_constant__ FineFwdParams p) {
+  constexpr bool kMerge = kMode == kModeMerge;
   extern __shared__ uint8_t smem_raw[];
   FwdSmem& sm = *reinterpret_cast<FwdSmem*>(smem_raw + ((1024 - (smem_u32(smem_raw) & 1023)) & 1023));
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -250,7 +258,7 @@ __global__ void __launch_bounds__(kThreads, 1) fine_fwd_kernel(const __grid_cons
     uint32_t buf_round = 0;  // parity of that buffer's current use
     for (int i = 0; i < pairs; ++i) {
       const uint32_t tmem_s = tmem + lane_base + buf * 128;
-      mbar_wait(&sm.s_done[buf], buf_round, abort_flag, p.status, 3);
+      mbar_wait(&sm.s_done[buf], buf_round, abort_flag, p.status, 4);
       tc_fence_after();
       // Valid keys among this thread's 32 (the K producer wrote the block sizes with the stage;
       // an odd list ends with half a pair, whose absent block has size 0).
@@ -329,7 +337,7 @@ __global__ void __launch_bounds__(kThreads, 1) fine_fwd_kernel(const __grid_cons
   }
 
   // ---------------------------------------------------------------- epilogue
-  if (warp < 8) {
+  if (warp < 8 && !(kMode == kModeRunning && n == 0)) {  // an empty ring step leaves the running state as it is
     const long long width = static_cast<long long>(p.heads) * kDim;
     l += __shfl_xor_sync(0xffffffffu, l, 16);
     if (half == 0) sm.l_part[group][row] = l;
@@ -341,49 +349,75 @@ __global__ void __launch_bounds__(kThreads, 1) fine_fwd_kernel(const __grid_cons
     const float l_all = sm.l_part[0][row] + sm.l_part[1][row];
     const float inv_l = l_all > 0.f ? 1.f / l_all : 0.f;
     const long long slot = static_cast<long long>(qb) * kBlock + row;
-    if (half == 0 && group == 0)
-      p.lse[static_cast<long long>(head) * p.q_slots + slot] = l_all > 0.f ? m_ref * p.scale + logf(l_all) : -INFINITY;
+    const float lse_new = l_all > 0.f ? m_ref * p.scale + logf(l_all) : -INFINITY;
     // Thread = (query row, 32 head dims): 64 contiguous bytes of one output row.
     const int dim0 = half * 64 + group * 32;
     const long long col = static_cast<long long>(head) * kDim + dim0;
-    long long out_row = -1;
-    const uint4* gate = nullptr;
-    const uint4* coarse = nullptr;
-    if (kMerge) {
-      out_row = p.slot_row != nullptr ? p.slot_row[slot] : slot;
-      if (out_row >= p.out_rows) out_row = -1;
-      const int coarse_slot = p.block_coarse != nullptr ? p.block_coarse[qb] : -1;
-      if (coarse_slot >= 0 && out_row >= 0) {
-        gate = reinterpret_cast<const uint4*>(p.gate + out_row * width + col);
-        coarse = reinterpret_cast<const uint4*>(p.coarse + coarse_slot * width + col);
-      }
-    }
-    uint4* o_dst = reinterpret_cast<uint4*>(p.o_slots + slot * width + col);
-    uint4* out_dst = (kMerge && out_row >= 0) ? reinterpret_cast<uint4*>(p.out + out_row * width + col) : nullptr;
     uint32_t o_bits[32] = {};
     if (n > 0) {
       VSA_TMEM_LD_16x32bx2_X32(o_bits, tmem + lane_base + kColO + group * 32, 64);
       tmem_wait_ld();
     }
+    if (kMode == kModeRunning) {
+      // running = (running * w_old + partial * w_new) / (w_old + w_new) with LSE weights; rows
+      // that have seen no key yet hold LSE = -inf and weight 0.
+      float* lse_at = p.lse + static_cast<long long>(head) * p.q_slots + slot;
+      const float lse_old = *lse_at;
+      float top = fmaxf(lse_old, lse_new);
+      if (top == -INFINITY) top = 0.f;
+      const float w_old = expf(lse_old - top), w_new = expf(lse_new - top);
+      const float denom = w_old + w_new;
+      const float inv = denom > 0.f ? 1.f / denom : 0.f;
+      const float f_old = w_old * inv, f_new = w_new * inv * inv_l;
+      named_barrier(1, kSoftmaxThreads);  // the four threads of a row have read the old LSE
+      if (half == 0 && group == 0) *lse_at = top + logf(denom);
+      float4* run = reinterpret_cast<float4*>(p.o_running + slot * width + col);
 #pragma unroll
-    for (int v4 = 0; v4 < 4; ++v4) {
-      float o[8];
-#pragma unroll
-      for (int e = 0; e < 8; ++e) o[e] = __uint_as_float(o_bits[v4 * 8 + e]) * inv_l;
-      o_dst[v4] = make_uint4(pack_bf16(o[0], o[1]), pack_bf16(o[2], o[3]), pack_bf16(o[4], o[5]), pack_bf16(o[6], o[7]));
-      if (kMerge && out_dst != nullptr) {
-        if (gate != nullptr) {
-          const uint4 g = gate[v4], cz = coarse[v4];
-          const uint32_t gw[4] = {g.x, g.y, g.z, g.w}, cw[4] = {cz.x, cz.y, cz.z, cz.w};
-#pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            const float2 gf = unpack_bf16(gw[e]), cf = unpack_bf16(cw[e]);
-            // Product and sum are rounded separately, as the reference's merge does.
-            o[2 * e] = __fadd_rn(o[2 * e], __fmul_rn(gf.x, cf.x));
-            o[2 * e + 1] = __fadd_rn(o[2 * e + 1], __fmul_rn(gf.y, cf.y));
-          }
+      for (int v4 = 0; v4 < 8; ++v4) {
+        const float4 old = run[v4];
+        float4 r;
+        r.x = (w_old > 0.f ? old.x * f_old : 0.f) + __uint_as_float(o_bits[v4 * 4 + 0]) * f_new;
+        r.y = (w_old > 0.f ? old.y * f_old : 0.f) + __uint_as_float(o_bits[v4 * 4 + 1]) * f_new;
+        r.z = (w_old > 0.f ? old.z * f_old : 0.f) + __uint_as_float(o_bits[v4 * 4 + 2]) * f_new;
+        r.w = (w_old > 0.f ? old.w * f_old : 0.f) + __uint_as_float(o_bits[v4 * 4 + 3]) * f_new;
+        run[v4] = r;
+      }
+    } else {
+      if (half == 0 && group == 0) p.lse[static_cast<long long>(head) * p.q_slots + slot] = lse_new;
+      long long out_row = -1;
+      const uint4* gate = nullptr;
+      const uint4* coarse = nullptr;
+      if (kMerge) {
+        out_row = p.slot_row != nullptr ? p.slot_row[slot] : slot;
+        if (out_row >= p.out_rows) out_row = -1;
+        const int coarse_slot = p.block_coarse != nullptr ? p.block_coarse[qb] : -1;
+        if (coarse_slot >= 0 && out_row >= 0) {
+          gate = reinterpret_cast<const uint4*>(p.gate + out_row * width + col);
+          coarse = reinterpret_cast<const uint4*>(p.coarse + coarse_slot * width + col);
         }
-        out_dst[v4] = make_uint4(pack_bf16(o[0], o[1]), pack_bf16(o[2], o[3]), pack_bf16(o[4], o[5]), pack_bf16(o[6], o[7]));
+      }
+      uint4* o_dst = reinterpret_cast<uint4*>(p.o_slots + slot * width + col);
+      uint4* out_dst = (kMerge && out_row >= 0) ? reinterpret_cast<uint4*>(p.out + out_row * width + col) : nullptr;
+#pragma unroll
+      for (int v4 = 0; v4 < 4; ++v4) {
+        float o[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) o[e] = __uint_as_float(o_bits[v4 * 8 + e]) * inv_l;
+        o_dst[v4] = make_uint4(pack_bf16(o[0], o[1]), pack_bf16(o[2], o[3]), pack_bf16(o[4], o[5]), pack_bf16(o[6], o[7]));
+        if (kMerge && out_dst != nullptr) {
+          if (gate != nullptr) {
+            const uint4 g = gate[v4], cz = coarse[v4];
+            const uint32_t gw[4] = {g.x, g.y, g.z, g.w}, cw[4] = {cz.x, cz.y, cz.z, cz.w};
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const float2 gf = unpack_bf16(gw[e]), cf = unpack_bf16(cw[e]);
+              // Product and sum are rounded separately, as the reference's merge does.
+              o[2 * e] = __fadd_rn(o[2 * e], __fmul_rn(gf.x, cf.x));
+              o[2 * e + 1] = __fadd_rn(o[2 * e + 1], __fmul_rn(gf.y, cf.y));
+            }
+          }
+          out_dst[v4] = make_uint4(pack_bf16(o[0], o[1]), pack_bf16(o[2], o[3]), pack_bf16(o[4], o[5]), pack_bf16(o[6], o[7]));
+        }
       }
     }
   }
@@ -396,7 +430,8 @@ size_t fine_fwd_smem_bytes() { return sizeof(FwdSmem) + 1024; }
 
 cudaError_t launch_fine_fwd(const FineFwdParams& params, bool merge, cudaStream_t stream) {
   const size_t smem = fine_fwd_smem_bytes();
-  auto kernel = merge ? fine_fwd_kernel<true> : fine_fwd_kernel<false>;
+  auto kernel = params.o_running != nullptr ? fine_fwd_kernel<kModeRunning>
+                                            : (merge ? fine_fwd_kernel<kModeMerge> : fine_fwd_kernel<kModePlain>);
   cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
   if (err != cudaSuccess) return err;
   dim3 grid(params.q_blocks, params.heads);

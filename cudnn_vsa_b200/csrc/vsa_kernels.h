@@ -19,6 +19,10 @@ struct FineFwdParams {
   const int32_t* kv_sizes;          // [kv_blocks] valid slots per KV block, or null (all 64)
   __nv_bfloat16* o_slots;           // [q_slots, heads, 128] normalised fine output
   float* lse;                       // [heads, q_slots]
+  // Ring step: when set, the partial result is folded into this running FP32 output
+  // ([q_slots, heads, 128], normalised) and `lse` is the running LSE, read and updated;
+  // o_slots and the merge fields are unused.
+  float* o_running;
   // merged output in caller row order (kMerge only)
   const int64_t* slot_row;          // [q_slots] caller row per slot (-1 = padding), null = identity
   const int32_t* block_coarse;      // [q_blocks] coarse row of each query block (-1 = none), or null

@@ -48,6 +48,7 @@ class _CoarsePlan:
     q_sizes: torch.Tensor       # int32 [q_rows/64]
     q_src: torch.Tensor         # int64 [q_rows]: local block whose token sits in each row, -1 = padding
     kv_src: torch.Tensor        # int64 [kv_rows]: source (global) block of each row, -1 = padding
+    block_kv_rows: torch.Tensor  # block_kv as an int64 row map for the row-gather kernel
 
 
 @dataclass
@@ -91,7 +92,8 @@ def _coarse_plan(pairs, q_blocks, kv_blocks, device):
         return src
     return _CoarsePlan(q_src=dev(inverse(block_q, q_chunks * BLOCK)), kv_src=dev(inverse(block_kv, kv_chunks * BLOCK)),
                        q_rows=q_chunks * BLOCK, kv_rows=kv_chunks * BLOCK, block_q=dev(block_q),
-                       block_kv=dev(block_kv), index=dev(index), counts=dev(counts),
+                       block_kv=dev(block_kv), block_kv_rows=dev(block_kv.astype(np.int64)), index=dev(index),
+                       counts=dev(counts),
                        kv_sizes=dev(np.asarray(kv_sizes or [0], dtype=np.int32)),
                        q_sizes=dev(np.asarray(q_sizes or [0], dtype=np.int32)))
 
@@ -158,13 +160,23 @@ def route(q_mean, k_mean, layout, plan=None):
         _cabi.call("vsa_route", _p(q_mean), _p(k_mean), heads, q_begin, q_end, 0, kv_first, kv_last, 0,
                    keep, cursor, _p(index), index.stride(1), cap, _p(scratch), scratch.numel(),
                    _cabi.stream(), launches=2 * passes)
-    plan.last_index = index
     return index
 
 
-def last_routing(layout):
-    """Routing table of the most recent forward pass of this layout (for FLOP accounting)."""
-    return getattr(device_plan(layout), "last_index", layout.routing_indices)
+def routing_table(q, k, layout):
+    """Routing table ``[1, H, B, cap]`` that a single-device forward pass on ``q, k`` (caller row
+    order) uses.  Pooling and selection are deterministic, so this reproduces the table of an
+    earlier call on the same inputs; benchmarks count useful FLOPs from it and tests hand it to
+    the oracle (reference ``vsa_core.py:75-84`` on the means of ``vsa_kernels.py:179-188``)."""
+    plan = device_plan(layout)
+    if not plan.spans:
+        return layout.routing_indices
+    heads, dim = q.shape[1], q.shape[2]
+    mean = torch.empty((3, layout.blocks, heads, dim), dtype=torch.float32, device=q.device)
+    _cabi.call("vsa_slots_pool", _p(q), _p(k), _p(k), None if layout.slots_are_input else _p(layout.slot_row),
+               _p(layout.block_sizes), None, None, None, _p(mean), None, None, 0, layout.blocks, heads,
+               _cabi.stream())
+    return route(mean[0], mean[1], layout, plan)
 
 
 def _fine_fwd(q, k, v, index, counts, head_strides, kv_sizes, scale, status, *, merge=None):

@@ -6,12 +6,15 @@ attention are global; the padded K/V token shard travels around the ring while t
 kernels work on the shard that is already here (reference ``vsa_core.py:123-315``).
 
 Schedule per forward step ``s`` (owner ``(rank - s) % R``): post the transfer of the current
-shard to ``rank + 1`` on a private stream, run ``vsa_fine_fwd`` on it with the owner's lists,
-fold the partial result into the FP32 running output with ``vsa_merge_partial``, then join the
-transfer.  The backward pass walks the ring in reverse starting from the last shard held, so the
-FP32 dK/dV that travel with each shard arrive home with the last step; ``vsa_fine_bwd`` adds dQ
-straight into the running FP32 buffer.  Collectives are NCCL through the borrowed process group;
-a remote shard always lands in this GPU's memory before any kernel reads it.
+shard to ``rank + 1`` on a private stream, run ``vsa_fine_fwd_running`` on it with the owner's
+lists - its epilogue folds the step's partial result into the FP32 running output and LSE, so
+no partial tensor is written and no merge pass runs - then join the transfer.  The backward pass
+walks the ring in reverse starting from the last shard held.  The FP32 dK/dV sums travel with
+their shard: each step posts the transfer, runs the dQ kernel (which adds into the running FP32
+dQ) under it, joins, and then runs the dK/dV kernel, which adds this rank's contribution
+straight into the buffer that just arrived; after ``R`` steps the sums are home.  No per-step
+allocation, no separate accumulation pass.  Collectives are NCCL through the borrowed process
+group; a remote shard always lands in this GPU's memory before any kernel reads it.
 """
 from __future__ import annotations
 
@@ -45,7 +48,11 @@ def ring_runtime(layout, device):
         batch_p2p = getattr(ring.group, "bound_device_id", None) is not None
     key = (str(device), batch_p2p)
     if key not in ring._runtime:
-        stream = torch.cuda.Stream(device=device) if torch.device(device).type == "cuda" else None
+        # The transfers are short next to the kernels they hide under; on a high-priority stream
+        # their CTAs are placed as soon as an SM frees up instead of queueing behind the grid of
+        # the compute kernel that was launched right after them.
+        stream = (torch.cuda.Stream(device=device, priority=-1)
+                  if torch.device(device).type == "cuda" else None)
         ring._runtime[key] = _RingRuntime(ring.group, ring.rank, ring.size, stream, batch_p2p,
                                           tuple(dist.get_process_group_ranks(ring.group)))
     return ring._runtime[key]
@@ -82,7 +89,8 @@ def ring_exchange(runtime, pairs, *, reverse=False):
 
 def join_exchange(runtime):
     if runtime.stream is not None:
-        torch.cuda.current_stream().wait_stream(runtime.stream)
+        with _cabi.mark("ring_exchange_wait"):
+            torch.cuda.current_stream().wait_stream(runtime.stream)
 
 
 def gather_means(k_mean, v_mean, runtime, global_to_gather):
@@ -179,11 +187,10 @@ class _RingVSAFunction(torch.autograd.Function):
             current = buffers[step % len(buffers)]
             if step + 1 < rt.size:
                 ring_exchange(rt, [(current, buffers[(step + 1) % 2])])
-            part, part_lse = _fine_fwd(q_s, current[0], current[1], lists[owner], counts[owner],
-                                       (lists.stride(1), counts.stride(1)), ring.peer_block_sizes[owner], scale,
-                                       plan.status)
-            _cabi.call("vsa_merge_partial", _p(out_f32), _p(lse), _p(part), _p(part_lse), slots, heads,
-                       _cabi.stream())
+            _cabi.call("vsa_fine_fwd_running", _p(q_s), _p(current[0]), _p(current[1]), blocks,
+                       current.shape[1] // BLOCK, heads, _p(lists[owner]), _p(counts[owner]), lists.stride(1),
+                       counts.stride(1), lists.shape[-1], _p(ring.peer_block_sizes[owner]), scale, _p(out_f32),
+                       _p(lse), _p(plan.status), _cabi.stream())
             if step + 1 < rt.size:
                 join_exchange(rt)
 
@@ -241,8 +248,8 @@ class _RingVSAFunction(torch.autograd.Function):
                            _p(mask), _p(dq_tok), _p(dk_tok), _p(dv_tok), tok_q.shape[0], tok_k.shape[0], None,
                            None, None, None, None, 0, None, None, None, None, None, 0, 7, _p(plan.status),
                            _cabi.stream(), launches=3)
-                block_kv = coarse.block_kv.long()
-                dk_global, dv_global = _gather_rows(dk_tok, block_kv), _gather_rows(dv_tok, block_kv)
+                dk_global = _gather_rows(dk_tok, coarse.block_kv_rows)
+                dv_global = _gather_rows(dv_tok, coarse.block_kv_rows)
             else:
                 dk_global = torch.zeros((total, heads, dim), dtype=torch.float32, device=device)
                 dv_global = torch.zeros_like(dk_global)
@@ -254,26 +261,29 @@ class _RingVSAFunction(torch.autograd.Function):
         dq_acc = torch.zeros((slots, heads, dim), dtype=torch.float32, device=device)
         words = _cabi.load().vsa_kv_mask_words(blocks)
         mask = torch.empty(heads * blocks * words, dtype=torch.int32, device=device)
+        # Two FP32 dK||dV buffers alternate: the sum that arrives at step s lands in sums[s % 2],
+        # the dK/dV kernel adds this rank's part to it in place, and step s + 1 sends it on.
+        sums = [torch.empty((2, slots, heads, dim), dtype=torch.float32, device=device)
+                for _ in range(min(rt.size, 2))]
         accumulated = None
-        incoming = torch.empty((2, slots, heads, dim), dtype=torch.float32, device=device) if rt.size > 1 else None
         for step in range(rt.size):
             owner = (rt.rank - (rt.size - 1 - step)) % rt.size
             current = buffers[step % len(buffers)]
+            target = sums[step % len(sums)]
             pairs = []
             if step + 1 < rt.size:
                 pairs.append((current, buffers[(step + 1) % 2]))
             if step:
-                pairs.append((accumulated, incoming))
+                pairs.append((accumulated, target))
             if pairs:
                 ring_exchange(rt, pairs, reverse=True)
-            part = torch.empty((2, slots, heads, dim), dtype=torch.float32, device=device)
             common = (q_s, current[0], current[1], grad_s, lists[owner], counts[owner], layout.block_sizes,
                       ring.peer_block_sizes[owner], scale, lse, delta, mask, plan.status)
             _bwd_call(*common, parts=3, dq_f32=dq_acc, accumulate=1)
-            _bwd_call(*common, parts=4, dk_f32=part[0], dv_f32=part[1], accumulate=0)
             if pairs:
                 join_exchange(rt)
-            accumulated = part.add_(incoming) if step else part
+            _bwd_call(*common, parts=4, dk_f32=target[0], dv_f32=target[1], accumulate=1 if step else 0)
+            accumulated = target
         dq, dk, dv = (torch.empty_like(grad) for _ in range(3))
         sizes = layout.block_sizes
         _cabi.call("vsa_grad_finish", _p(dq_acc), _p(layout.slot_row), _p(dq_tok), 0,
@@ -283,6 +293,22 @@ class _RingVSAFunction(torch.autograd.Function):
             _cabi.call("vsa_grad_finish", _p(acc), _p(layout.slot_row), _p(pool), 1, None, _p(sizes), _p(out),
                        blocks, heads, tokens, _cabi.stream())
         return dq, dk, dv, dgate, None, None
+
+
+def routing_table(q, k, layout):
+    """Routing table of this rank's query blocks over global KV block ids, as the ring forward
+    pass computes it (pooling, all-gather of the pooled K, selection).  A collective: every rank
+    of the group must call it.  Benchmarks count useful FLOPs from it."""
+    rt = ring_runtime(layout, q.device)
+    plan = device_plan(layout)
+    if layout.dense_only:
+        return layout.routing_indices
+    heads, dim = q.shape[1], q.shape[2]
+    mean = torch.empty((3, layout.blocks, heads, dim), dtype=torch.float32, device=q.device)
+    _cabi.call("vsa_slots_pool", _p(q), _p(k), _p(k), _p(layout.slot_row), _p(layout.block_sizes), None, None, None,
+               _p(mean), None, None, 0, layout.blocks, heads, _cabi.stream())
+    k_all, _ = gather_means(mean[1], mean[2], rt, layout.ring.global_to_gather)
+    return route(mean[0], k_all, layout, plan)
 
 
 def ring_attention(q, k, v, gate, layout, *, scale=None):

@@ -2,9 +2,14 @@
  *
  * Conventions
  *   - Every pointer is a device pointer unless stated; the library never allocates, frees or
- *     synchronises, keeps no mutable global state, and launches on the stream it is given
- *     (`stream` is a cudaStream_t passed as void*).  The caller allocates every output and
- *     every scratch buffer (sizes below).
+ *     synchronises, and launches on the stream it is given (`stream` is a cudaStream_t passed as
+ *     void*).  The caller allocates every output and every scratch buffer (sizes below), and the
+ *     library keeps no mutable global state - with ONE exception, `vsa_route_static`: it works
+ *     in a 16 MiB device array that is part of the library image and caches that array's
+ *     address per device on the host.  Its first call on a device may make the CUDA runtime
+ *     load the module that holds the array (CUDA loads modules lazily), which reserves the
+ *     16 MiB at that moment; make that call during set-up, before any stream capture and before
+ *     any region of the program that must not allocate.
  *   - Activations are BF16, row-major `[rows, heads, 128]`; a "slot" tensor holds `blocks * 64`
  *     rows (64 zero-padded slots per block).  `width = heads * 128`.
  *   - Return value: 0 on success, otherwise a VSA_STATUS_* code (a CUDA launch error leaves the
@@ -71,15 +76,16 @@ int vsa_route(const float* q_mean, const float* k_mean, int32_t heads, int32_t q
 /* vsa_route without a scratch argument, for callers that may not allocate device memory (a
  * runtime plugin whose enqueue hook must not allocate, a process whose device memory belongs to
  * another framework's pool).  No counterpart in the reference, which allocates freely through
- * PyTorch.  The score matrix lives in a 16 MiB array inside the library's device image (held by
- * every GPU that loads the library, from load to exit).  One head's scores,
+ * PyTorch.  The score matrix lives in a 16 MiB array inside the library's device image, held by
+ * every GPU that uses this entry point from its first call on that GPU to process exit (see the
+ * conventions above about lazy module loading).  One head's scores,
  * (q_end - q_begin) * (kv_last - kv_first) * 4 bytes, must fit in it, otherwise the call returns
  * VSA_STATUS_STATIC_SCRATCH and does nothing; heads beyond what fits run in further passes.
- * The call allocates and frees nothing.  All calls on a device share the array (it keeps the
- * last call's contents; nothing in it needs clearing because each call writes every score it
- * reads), so calls that overlap on the GPU race - keep them on one stream.  The first call on a
- * device queries the array's address on the host; make it before any stream capture begins.
- * Results are identical to vsa_route. */
+ * The first call on a device queries the array's address on the host: make it during set-up,
+ * before any stream capture begins.  After it, a call allocates and frees nothing.  All calls on
+ * a device share the array (it keeps the last call's contents; nothing in it needs clearing
+ * because each call writes every score it reads), so calls that overlap on the GPU race - keep
+ * them on one stream.  Results are identical to vsa_route. */
 int vsa_route_static(const float* q_mean, const float* k_mean, int32_t heads, int32_t q_begin, int32_t q_end,
                      int32_t q_mean_offset, int32_t kv_first, int32_t kv_last, int32_t k_mean_offset, int32_t keep,
                      int32_t cursor, int32_t* indices, int64_t index_head_stride, int32_t capacity, void* stream);
@@ -107,6 +113,18 @@ int vsa_fine_fwd(const void* q, const void* k, const void* v, int64_t q_blocks, 
                  int32_t capacity, const int32_t* kv_sizes, float scale, void* o_slots, float* lse,
                  const int64_t* slot_row, const int32_t* block_coarse, const void* gate, const void* coarse,
                  void* out, int64_t out_rows, int32_t* status, void* stream);
+
+/* Ring step of the forward pass: vsa_fine_fwd on the shard that is here, with the online-softmax
+ * merge into the running result done in the kernel's epilogue.  o_running [q_blocks*64, heads, 128]
+ * FP32 holds the normalised result of the steps so far (zero before the first) and lse_running
+ * [heads, q_blocks*64] their LSE (-inf before the first); both are read and updated in place.  A
+ * query block whose list is empty at this step leaves its rows untouched.
+ * Replaces vsa_core.py:234-240 (cuDNN BSA forward of the step + `_merge_partial`,
+ * vsa_kernels.py:375-397). */
+int vsa_fine_fwd_running(const void* q, const void* k, const void* v, int64_t q_blocks, int64_t kv_blocks,
+                         int32_t heads, const int32_t* indices, const int32_t* counts, int64_t index_head_stride,
+                         int64_t count_head_stride, int32_t capacity, const int32_t* kv_sizes, float scale,
+                         float* o_running, float* lse_running, int32_t* status, void* stream);
 
 /* Adjoint of the gate merge fused with the slot gather of dO and with delta = rowsum(dO * O_fine).
  *   grad [rows, width] BF16 in caller order -> grad_slots [blocks*64, width] (null: not wanted),

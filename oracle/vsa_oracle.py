@@ -107,26 +107,38 @@ def keep_count(sparsity, blocks):
     return max(1, math.ceil((1 - sparsity) * blocks))
 
 
-def route(q_mean, k_mean, layout):
+def route(q_mean, k_mean, layout, query_blocks=None):
     """Fill the routing template: per video region that needs selection, per (head, query
     block), the ``keep`` highest unscaled FP32 scores ``q_mean . k_mean`` listed in
     ascending block order (reference ``vsa_core.py:61-84``).
 
     ``q_mean`` / ``k_mean`` are ``[pooled_blocks, H, D]`` float32 in the layout's pooled index
-    space (``routing_groups`` carries the offset).  Returns ``[1, H, B, cap]`` int32.
+    space (``routing_groups`` carries the offset).  Returns ``[1, H, B, cap]`` int32, or only the
+    rows of ``query_blocks`` (a 1-D tensor of block ids) when a bounded sample is wanted.
     """
-    if not layout.routing_groups:
-        return layout.routing_indices
-    index = layout.routing_indices.clone()
+    if query_blocks is None:
+        if not layout.routing_groups:
+            return layout.routing_indices
+        index = layout.routing_indices.clone()
+    else:
+        index = layout.routing_indices[:, :, query_blocks].clone()
     for group, begin, end, offset in layout.routing_groups:
-        queries = q_mean[begin + offset:end + offset].float().transpose(0, 1)  # [H, nq, D]
+        if query_blocks is None:
+            rows = slice(begin, end)
+            queries = q_mean[begin + offset:end + offset]
+        else:
+            rows = (query_blocks >= begin) & (query_blocks < end)
+            if not bool(rows.any()):
+                continue
+            queries = q_mean[query_blocks[rows] + offset]
+        queries = queries.float().transpose(0, 1)  # [H, nq, D]
         cursor = group.dense_blocks_num
         for first, last, keep in group.video_spans:
             if keep < last - first:
                 keys = k_mean[first + offset:last + offset].float().permute(1, 2, 0)  # [H, D, span]
                 scores = queries @ keys
                 chosen = scores.topk(keep, dim=-1, sorted=False).indices.sort(-1).values
-                index[0, :, begin:end, cursor:cursor + keep] = (chosen + first).to(torch.int32)
+                index[0][:, rows, cursor:cursor + keep] = (chosen + first).to(torch.int32)
             cursor += keep
     return index
 
@@ -154,15 +166,18 @@ def fine_attention(q, k, v, indices, counts, sizes, scale):
     Same contract as the reference's fine backend call (``vsa_core.py:15-20``; dense CPU
     substitute ``tests/reference.py:57-67``) but evaluated block by block, so it scales to
     long sequences.  ``q, k, v`` are ``[P, H, D]`` slot tensors; ``indices [1,H,B,cap]``,
-    ``counts [1,H,B]``.  Returns ``(out [P,H,D] float32, lse [H,P] float32)``; a query block
-    with an empty list gives zeros and ``-inf``.
+    ``counts [1,H,B]``.  ``q`` may hold fewer blocks than ``k`` (a sample of query blocks with
+    their rows of the table).  All tensors live on one device; a test may place them on a GPU
+    when it needs this FP32 restatement at sizes the CPU cannot finish in seconds.
+    Returns ``(out [P,H,D] float32, lse [H,P] float32)``; a query block with an empty list gives
+    zeros and ``-inf``.
     """
     slots, heads, dim = q.shape
     blocks = slots // BLOCK
     qf, kf, vf = (x.float().view(-1, BLOCK, heads, dim) for x in (q, k, v))
-    size_of = (torch.full((kf.shape[0],), BLOCK, dtype=torch.int64) if sizes is None
+    size_of = (torch.full((kf.shape[0],), BLOCK, dtype=torch.int64, device=q.device) if sizes is None
                else sizes.to(torch.int64))
-    slot_ids = torch.arange(BLOCK)
+    slot_ids = torch.arange(BLOCK, device=q.device)
     outs = [[None] * blocks for _ in range(heads)]
     lses = [[None] * blocks for _ in range(heads)]
     count_host = counts[0].tolist()

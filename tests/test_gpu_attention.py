@@ -85,12 +85,38 @@ def test_routing_matches_oracle_and_reference(name, dense_query_full):
         assert routing_mismatches_are_near_ties(got, torch.from_numpy(cases[key]), scores, counts)
 
 
+def test_routing_of_a_14720_block_region_in_several_head_passes():
+    """The region of the ring configuration: 14,720 scores per row (more than the 48 KiB of static
+    shared memory, so the selection kernel runs with its opt-in size) and 737 kept.  The scratch
+    holds one head's score matrix, so the three heads take three passes."""
+    heads, rows, region, keep = 3, 8, 14720, 737
+    gen = torch.Generator().manual_seed(5)
+    q_mean = torch.randn(rows, heads, 128, generator=gen) * 0.2
+    k_mean = torch.randn(region, heads, 128, generator=gen) * 0.2
+    index = torch.zeros((1, heads, rows, keep), dtype=torch.int32, device="cuda")
+    scratch = torch.empty(rows * region * 4, dtype=torch.uint8, device="cuda")
+    dq, dk = q_mean.cuda(), k_mean.cuda()
+    _cabi.call("vsa_route", _cabi.ptr(dq), _cabi.ptr(dk), heads, 0, rows, 0, 0, region, 0, keep, 0,
+               _cabi.ptr(index), index.stride(1), keep, _cabi.ptr(scratch), scratch.numel(), _cabi.stream(),
+               launches=2 * heads)
+    got = index.cpu()
+    scores = torch.einsum("qhd,khd->hqk", q_mean, k_mean)
+    want = scores.topk(keep, dim=-1, sorted=False).indices.sort(-1).values.to(torch.int32)[None]
+    assert (got[..., 1:] > got[..., :-1]).all(), "ascending, duplicate-free"
+    assert got.min() >= 0 and got.max() < region
+    spans = [(0, rows, 0, region, keep, 0, scores)]
+    assert routing_mismatches_are_near_ties(got, want, spans, None)
+    assert (got == want).float().mean().item() > 0.999
+
+
 def _random_lists(heads, q_blocks, kv_blocks, cap, gen):
     index = torch.zeros((1, heads, q_blocks, cap), dtype=torch.int32)
     counts = torch.zeros((1, heads, q_blocks), dtype=torch.int32)
     for h in range(heads):
         for b in range(q_blocks):
             n = int(torch.randint(0 if b == 1 else 1, min(cap, kv_blocks) + 1, (1,), generator=gen))
+            if b == 0 and h == 0:
+                n = min(cap, kv_blocks)  # one list of full length in every case
             ids = torch.randperm(kv_blocks, generator=gen)[:n].sort().values
             index[0, h, b, :n] = ids.to(torch.int32)
             counts[0, h, b] = n
@@ -99,8 +125,10 @@ def _random_lists(heads, q_blocks, kv_blocks, cap, gen):
 
 # List lengths from 0 to `cap`: every tail of the pair / stage / buffer rings (odd lists, one pair
 # only, lengths around the ring wrap points) occurs in some (head, query block).
+# The last case has the list length of the ring configuration (801 blocks: 401 pairs, every ring
+# of stages and buffers wraps more than a hundred times) and more than two mask words.
 @pytest.mark.parametrize("heads,q_blocks,kv_blocks,cap", [(1, 2, 3, 3), (2, 5, 9, 6), (3, 4, 40, 33), (2, 24, 20, 15),
-                                                           (1, 9, 70, 64)])
+                                                           (1, 9, 70, 64), (1, 3, 900, 801), (5, 70, 6, 6)])
 def test_fine_forward_and_backward_on_given_lists(heads, q_blocks, kv_blocks, cap):
     gen = torch.Generator().manual_seed(11)
     q = torch.randn(q_blocks * BLOCK, heads, 128, generator=gen).to(torch.bfloat16)
@@ -121,7 +149,7 @@ def test_fine_forward_and_backward_on_given_lists(heads, q_blocks, kv_blocks, ca
     dev = [x.cuda() for x in (q, k, v, d_o, index, counts, sizes)]
     strides = (dev[4].stride(1), dev[5].stride(1))
     o, lse = vsa_core._fine_fwd(dev[0], dev[1], dev[2], dev[4], dev[5], strides, dev[6], scale, status)
-    assert_close(o, want_o, "fine out")
+    assert_close(o.cpu(), want_o, "fine out")
     live = torch.isfinite(want_lse)
     assert torch.equal(torch.isfinite(lse.cpu()), live)
     torch.testing.assert_close(lse.cpu()[live], want_lse[live], atol=2e-3, rtol=1e-3)
@@ -130,9 +158,9 @@ def test_fine_forward_and_backward_on_given_lists(heads, q_blocks, kv_blocks, ca
     dq, dk, dv = vsa_core._fine_bwd(dev[0], dev[1], dev[2], dev[3], dev[4], dev[5], strides, q_sizes,
                                     dev[6], scale, lse, delta, status)
     assert int(status.item()) == 0
-    assert_close(dq, want_dq, "dq")
-    assert_close(dk.cpu()[valid], want_dk[valid], "dk")
-    assert_close(dv.cpu()[valid], want_dv[valid], "dv")
+    assert_close(dq.cpu(), want_dq, "dq")
+    assert_close(dk.cpu()[valid], want_dk[valid], "dk", peak_relative=True)
+    assert_close(dv.cpu()[valid], want_dv[valid], "dv", peak_relative=True)
 
 
 def _run(layout, q, k, v, gate, dy):
@@ -165,34 +193,51 @@ def test_attention_against_fp32_oracle(name, order):
     leaves = [x.float().requires_grad_() for x in (q, k, v, gate)]
     want, _ = vsa_oracle.vsa_attention(*leaves, cpu_layout, indices=index.cpu())
     want_grads = torch.autograd.grad(want, leaves, dy.float(), allow_unused=True)
-    assert_close(out, want, f"{name} out")
+    assert_close(out.cpu(), want, f"{name} out")
     for tag, got, ref in zip(("dq", "dk", "dv", "dgate"), grads, want_grads):
         if tag == "dgate" and layout.dense_only:
             assert got is None
             continue
         ref = torch.zeros_like(q, dtype=torch.float32) if ref is None else ref.nan_to_num()
-        assert_close(got, ref, f"{name} {tag}")
+        assert_close(got.cpu(), ref, f"{name} {tag}", peak_relative=tag in ("dk", "dv"))
 
 
 @pytest.mark.parametrize("name", SMALL)
 def test_attention_against_reference_golden_vectors(name):
+    """Output and gradients against the vectors of the reference's own CPU code.  Those carry the
+    reference's top-k choices: where the kernel's routing table differs from the stored one (a
+    near-tie, checked by the routing test), the rows of the query blocks whose lists differ are
+    left out for out / dq / dgate, and the rows of every KV block on such a list for dk / dv.
+    Everything else must meet the stated bounds."""
     heads = 2
     cases = golden_cases()
     layout = build_vsa_layout(GEOMETRIES[name], head_num=heads, device="cuda")
     q, k, v, gate = seeded(layout.tokens, heads, 0, 4)
     dy, = seeded(layout.tokens, heads, 1, 1)
     out, grads = _run(layout, q, k, v, gate, dy)
+    index = layout.routing_indices
+    if vsa_core.device_plan(layout).spans:
+        _, mean, _ = _pooled(layout, q.cuda(), k.cuda(), v.cuda())
+        index = vsa_core.route(mean[0], mean[1], layout)
+    index, counts = index.cpu(), layout.routing_counts.cpu()
+    key = f"{name}/dqf0/routing"
+    stored = torch.from_numpy(cases[key]) if key in cases.files else index
+    listed = torch.arange(index.shape[-1]) < counts[..., None]
+    differ = ((index != stored) & listed).any(-1)[0]          # [heads, blocks]
+    skip_q = differ.any(0)
+    skip_kv = torch.zeros(layout.blocks, dtype=torch.bool)
+    for h, b in differ.nonzero().tolist():
+        for table in (index, stored):
+            skip_kv[table[0, h, b, :counts[0, h, b]].long()] = True
+    assert skip_q.float().mean().item() <= 0.1, "routing differs from the reference on too many query blocks"
+    row_block = (layout.row_slot.cpu() // BLOCK).long()
     stride = 4 if layout.tokens > 600 else 1
-    key = f"{name}/dqf0/pack"
-    # The golden vectors carry the reference's own top-k choices; a near-tie flip changes whole
-    # rows, so compare with a bound on the fraction of rows that may differ.
     for tag, got in zip(("out", "dq", "dk", "dv", "dgate"), (out, *grads)):
-        want = from_bits(cases[f"{key}/{tag}"]).float()
-        got = (torch.zeros_like(q).cuda() if got is None else got)[::stride].float().cpu()
-        row_err = (got - want).abs().amax(dim=(1, 2))
-        assert (row_err > 4e-2).float().mean().item() <= 0.02, (tag, row_err.max().item())
-        good = row_err <= 4e-2
-        assert_close(got[good], want[good], f"{name} {tag} vs reference", max_abs=4e-2, rel_l2=1.5e-2)
+        want = from_bits(cases[f"{name}/dqf0/pack/{tag}"]).float()
+        got = (torch.zeros_like(q).cuda() if got is None else got).float().cpu()
+        keep = ~(skip_kv if tag in ("dk", "dv") else skip_q)[row_block]
+        assert_close(got[::stride][keep[::stride]], want[keep[::stride]], f"{name} {tag} vs reference",
+                     peak_relative=tag in ("dk", "dv"))
 
 
 def test_cuda_graph_capture_and_replay_with_changed_inputs():

@@ -1,14 +1,20 @@
-"""GPU: the configurations named for the benchmark at their full sizes, checked through
-properties that do not need a full-size oracle: sampled blocks against the CPU oracle, exact row
-maps on wide rows, linearity of the gate term and of the backward pass, fine-only samples."""
+"""GPU: the benchmark configurations at their stated sizes (heads included).
+
+Value parity: output and all four gradients of ``vsa_attention`` against the FP32 oracle for a
+subset of heads over EVERY row (``tests.helpers.oracle_heads`` runs the oracle's blockwise fine
+attention, pooling, coarse attention and merge in FP32 on the GPU, chunk by chunk, with the
+routing table the kernels used).  Bounds are the stated ones, max-abs 2e-2 and relative L2 1e-2;
+only dk / dv use the peak-relative max-abs form (see ``assert_close``), and each test prints what
+every tensor needed.  Properties that need no oracle: exact row maps on wide rows, fine-only
+samples that never read the gate, raster and block order giving the same result.
+"""
 import pytest
 import torch
 
-from cudnn_vsa_b200 import _cabi, vsa_core
+from cudnn_vsa_b200 import vsa_core
 from cudnn_vsa_b200.vsa import block_wo_padding_to_raster, raster_to_block_wo_padding, vsa_attention
-from cudnn_vsa_b200.vsa_layout import BLOCK, build_vsa_layout
-from oracle import vsa_oracle
-from tests.helpers import GEOMETRIES, assert_close
+from cudnn_vsa_b200.vsa_layout import build_vsa_layout
+from tests.helpers import GEOMETRIES, REPORT, assert_close, oracle_heads
 
 pytestmark = pytest.mark.gpu
 
@@ -19,79 +25,57 @@ def _inputs(tokens, heads, count, seed=0):
             for _ in range(count)]
 
 
-def test_single_720p_sample_sampled_blocks_match_oracle():
+def _check_call(layout, q, k, v, gate, dy, use_heads, label):
+    """One forward + backward of the CUDA path against the FP32 oracle on ``use_heads``."""
+    leaves = [x.detach().clone().requires_grad_() for x in (q, k, v, gate)]
+    out = vsa_attention(*leaves, layout)
+    grads = torch.autograd.grad(out, leaves, dy, allow_unused=True)
+    vsa_core.check_status(layout)
+    index = vsa_core.routing_table(q, k, layout)
+    want = oracle_heads(q, k, v, gate, dy, layout, index, use_heads)
+    first = len(REPORT)
+    for tag, got, ref in zip(("out", "dq", "dk", "dv", "dgate"), (out, *grads), want):
+        if ref is None:
+            assert got is None
+            continue
+        assert_close(got[:, use_heads].float(), ref, f"{label} {tag}", peak_relative=tag in ("dk", "dv"))
+    for what, err, bound, rel, peak, relative in REPORT[first:]:
+        print(f"PARITY {what}: max_abs={err:.3e} bound={bound:.3e} rel_l2={rel:.3e} peak={peak:.3g} "
+              f"{'peak-relative' if relative else 'absolute'} heads={list(use_heads)}")
+    return out, grads, index
+
+
+def test_single_720p_sample_h12_values_and_gradients():
     heads = 12
     layout = build_vsa_layout(GEOMETRIES["c2"], head_num=heads, device="cuda")
-    q, k, v, gate, dy = _inputs(layout.tokens, heads, 5)
-    leaves = [x.requires_grad_() for x in (q, k, v, gate)]
-    out = vsa_attention(*leaves, layout)
-    grads = torch.autograd.grad(out, leaves, dy)
-    vsa_core.check_status(layout)
-    assert all(torch.isfinite(t).all() for t in (out, *grads))
-    index = vsa_core.last_routing(layout)
+    q, k, v, gate = _inputs(layout.tokens, heads, 4)
+    dy = _inputs(layout.tokens, heads, 1, seed=1)[0]
+    _, _, index = _check_call(layout, q, k, v, gate, dy, [0, 5, 11], "720p_single_sample_h12")
     counts = layout.routing_counts
     assert int(counts.min()) == int(counts.max()) == 224
-    valid_rows = index[0]
-    assert (valid_rows[..., 1:] > valid_rows[..., :-1]).all(), "ascending, duplicate-free lists"
-    assert (valid_rows[..., :32] == torch.arange(32, device="cuda")).all(), "dense blocks always listed"
-    # Fine attention of a few query blocks and heads, recomputed by the oracle from the same slots.
-    plan = vsa_core.device_plan(layout)
-    slots = [torch.empty((layout.padded_tokens, heads, 128), dtype=q.dtype, device="cuda") for _ in range(3)]
-    _cabi.call("vsa_slots_pool", _cabi.ptr(q), _cabi.ptr(k), _cabi.ptr(v), _cabi.ptr(layout.slot_row),
-               _cabi.ptr(layout.block_sizes), *(_cabi.ptr(s) for s in slots), None, None, None, 0,
-               layout.blocks, heads, _cabi.stream())
-    strides = (index.stride(1), counts.stride(1))
-    fine, lse = vsa_core._fine_fwd(slots[0], slots[1], slots[2], index, counts, strides, plan.sizes,
-                                   128 ** -0.5, plan.status)
-    picked = torch.tensor([0, 31, 32, 700, 1500, 1951])
-    use_heads = [0, 7]
-    rows = (picked[:, None] * BLOCK + torch.arange(BLOCK)[None, :]).reshape(-1)
-    q_sub = slots[0][rows.cuda()][:, use_heads].cpu()
-    k_cpu, v_cpu = (s[:, use_heads].cpu() for s in slots[1:])
-    sub_index = index[:, use_heads][:, :, picked.cuda()].cpu().contiguous()
-    sub_counts = counts[:, use_heads][:, :, picked.cuda()].cpu().contiguous()
-    want, want_lse = vsa_oracle.fine_attention(q_sub, k_cpu, v_cpu, sub_index, sub_counts,
-                                               layout.block_sizes.cpu(), 128 ** -0.5)
-    assert_close(fine[rows.cuda()][:, use_heads], want, "sampled fine output")
-    torch.testing.assert_close(lse[use_heads][:, rows.cuda()].cpu(), want_lse, atol=2e-3, rtol=1e-3)
+    rows = index[0]
+    assert (rows[..., 1:] > rows[..., :-1]).all(), "ascending, duplicate-free lists"
+    assert (rows[..., :32] == torch.arange(32, device="cuda")).all(), "dense blocks always listed"
 
 
-def test_packed_sample_gate_term_backward_linearity_and_fine_only_samples():
-    heads = 4
+def test_packed_720p_sample_h24_values_gradients_and_fine_only_samples():
+    heads = 24
     layout = build_vsa_layout(GEOMETRIES["c3"], head_num=heads, device="cuda")
-    q, k, v, gate, dy = _inputs(layout.tokens, heads, 5)
+    q, k, v, gate = _inputs(layout.tokens, heads, 4)
+    dy = _inputs(layout.tokens, heads, 1, seed=1)[0]
     dense_rows = slice(layout.sample_lengths[0], layout.tokens)  # samples 1 and 2 are fine-only
     assert layout.groups[1].dense_only and layout.groups[2].dense_only
-    base = vsa_attention(q, k, v, torch.zeros_like(gate), layout)
-    with_gate = vsa_attention(q, k, v, gate, layout)
+    out, grads, _ = _check_call(layout, q, k, v, gate, dy, [0, 13, 23], "720p_packed_sample_h24")
     poisoned = gate.clone()
     poisoned[dense_rows] = float("nan")
-    assert torch.equal(vsa_attention(q, k, v, poisoned, layout), with_gate), "fine-only rows never read gate"
-    assert torch.equal(with_gate[dense_rows], base[dense_rows])
-    # out - out(gate=0) = gate * coarse[block]: dividing by the gate recovers one coarse row per block.
-    vsa_rows = slice(0, layout.sample_lengths[0])
-    ratio = (with_gate[vsa_rows].float() - base[vsa_rows].float()) / gate[vsa_rows].float()
-    block_of_row = (layout.row_slot[vsa_rows] // BLOCK).long()
-    strong = gate[vsa_rows].float().abs() > 1.0
-    ratio = torch.where(strong, ratio, torch.zeros_like(ratio))
-    sums = torch.zeros((layout.blocks, heads, 128), device="cuda").index_add_(0, block_of_row, ratio)
-    cnt = torch.zeros((layout.blocks, heads, 128), device="cuda").index_add_(0, block_of_row, strong.float())
-    mean = sums / cnt.clamp_min(1)
-    spread = torch.where(strong, ratio - mean[block_of_row], torch.zeros_like(ratio)).abs().max().item()
-    assert spread < 6e-2, spread  # BF16 rounding of out and out(0) divided by |gate| > 1
-    # The backward pass is linear in dO.
-    leaves = [x.clone().requires_grad_() for x in (q, k, v, gate)]
-    out = vsa_attention(*leaves, layout)
-    g1 = torch.autograd.grad(out, leaves, dy, retain_graph=True)
-    g2 = torch.autograd.grad(out, leaves, dy * 2)
-    for a, b, name in zip(g1, g2, ("dq", "dk", "dv", "dgate")):
-        assert_close(b, a.float() * 2, f"linearity {name}", max_abs=2e-2, rel_l2=6e-3)
-    assert not g1[3][dense_rows].count_nonzero(), "no gate gradient on fine-only samples"
+    assert torch.equal(vsa_attention(q, k, v, poisoned, layout), out), "fine-only rows never read gate"
+    assert torch.equal(vsa_attention(q, k, v, torch.zeros_like(gate), layout)[dense_rows], out[dense_rows])
+    assert not grads[3][dense_rows].count_nonzero(), "no gate gradient on fine-only samples"
     vsa_core.check_status(layout)
 
 
-def test_block_order_stack_reuses_one_layout_and_reorders_wide_rows_exactly():
-    heads = 4
+def test_block_order_stack_h24_eight_layers_one_layout():
+    heads, layers = 24, 8
     layout = build_vsa_layout(GEOMETRIES["c4"], head_num=heads, device="cuda", input_order="block")
     tokens = layout.tokens
     hidden = torch.randn(tokens, 3072, device="cuda", dtype=torch.bfloat16)
@@ -101,18 +85,28 @@ def test_block_order_stack_reuses_one_layout_and_reorders_wide_rows_exactly():
     assert torch.equal(hidden_b, hidden[layout.input_rows]) and torch.equal(position_b, position[layout.input_rows])
     assert torch.equal(block_wo_padding_to_raster(hidden_b, vsa_layout=layout), hidden)
     assert torch.equal(block_wo_padding_to_raster(position_b, vsa_layout=layout), position)
-    # Three stacked calls through one layout, block-ordered activations, gradients through all.
+    del hidden, hidden_b
+    # Eight stacked calls through one layout on block-ordered activations, gradients through all.
     x = _inputs(tokens, heads, 1, seed=3)[0].requires_grad_()
-    y = x
-    for layer in range(3):
-        y = vsa_attention(y, y, y, torch.full_like(y, 0.5), layout)
+    gate = torch.full_like(x, 0.5)
+    y, last_input = x, None
+    for layer in range(layers):
+        last_input = y
+        y = vsa_attention(y, y, y, gate, layout)
     grad, = torch.autograd.grad(y, x, torch.ones_like(y))
     assert torch.isfinite(y).all() and torch.isfinite(grad).all()
-    # Same stack in raster order gives the same result after reordering.
-    raster_layout = build_vsa_layout(GEOMETRIES["c4"], head_num=heads, device="cuda")
-    xr = block_wo_padding_to_raster(x.detach(), vsa_layout=layout)
-    yr = xr
-    for layer in range(3):
-        yr = vsa_attention(yr, yr, yr, torch.full_like(yr, 0.5), raster_layout)
-    assert_close(raster_to_block_wo_padding(yr, vsa_layout=layout), y, "raster vs block order stack")
     vsa_core.check_status(layout)
+    # The same stack in raster order gives the same result after reordering.
+    raster_layout = build_vsa_layout(GEOMETRIES["c4"], head_num=heads, device="cuda")
+    with torch.no_grad():
+        yr = block_wo_padding_to_raster(x.detach(), vsa_layout=layout)
+        gate_r = torch.full_like(yr, 0.5)
+        for layer in range(layers):
+            yr = vsa_attention(yr, yr, yr, gate_r, raster_layout)
+    assert_close(raster_to_block_wo_padding(yr, vsa_layout=layout), y, "raster vs block order, 8 layers")
+    del yr, gate_r, grad
+    # Values and gradients of the last layer's call on the activations that reach it.
+    act = last_input.detach()
+    dy = _inputs(tokens, heads, 1, seed=1)[0]
+    _check_call(layout, act, act.clone(), act.clone(), _inputs(tokens, heads, 1, seed=4)[0], dy, [0, 23],
+                "block_order_stack_h24 layer 8")

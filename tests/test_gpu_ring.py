@@ -83,11 +83,22 @@ def test_ring_steps_replayed_on_one_gpu(name, size, partition, metadata_group):
         lse = torch.full((heads, slots), float("-inf"), device="cuda")
         status = vsa_core.device_plan(lay).status
         strides = (lists.stride(1), counts.stride(1))
+        # Two ways to the same running state: the ring step kernel that merges in its epilogue,
+        # and the plain forward kernel followed by the separate merge kernel.
+        out2, lse2 = out.clone(), lse.clone()
         for step in range(size):
             owner = (rank - step) % size
-            part, part_lse = vsa_core._fine_fwd(q_s, shards[owner][0][1], shards[owner][0][2], lists[owner],
-                                                counts[owner], strides, lay.ring.peer_block_sizes[owner], scale, status)
-            _cabi.call("vsa_merge_partial", p(out), p(lse), p(part), p(part_lse), slots, heads, _cabi.stream())
+            k_o, v_o = shards[owner][0][1], shards[owner][0][2]
+            _cabi.call("vsa_fine_fwd_running", p(q_s), p(k_o), p(v_o), lay.blocks, k_o.shape[0] // BLOCK, heads,
+                       p(lists[owner]), p(counts[owner]), strides[0], strides[1], lists.shape[-1],
+                       p(lay.ring.peer_block_sizes[owner]), scale, p(out), p(lse), p(status), _cabi.stream())
+            part, part_lse = vsa_core._fine_fwd(q_s, k_o, v_o, lists[owner], counts[owner], strides,
+                                                lay.ring.peer_block_sizes[owner], scale, status)
+            _cabi.call("vsa_merge_partial", p(out2), p(lse2), p(part), p(part_lse), slots, heads, _cabi.stream())
+        assert_close(out2, out, f"rank {rank} merge kernel vs merging epilogue", max_abs=1e-2, rel_l2=5e-3)
+        assert torch.equal(torch.isfinite(lse2), torch.isfinite(lse))
+        live = torch.isfinite(lse)
+        torch.testing.assert_close(lse2[live], lse[live], atol=2e-3, rtol=1e-3)
         rows = (ids[owned, None] * BLOCK + torch.arange(BLOCK, device="cuda")).flatten()
         mine = torch.arange(int(owned.sum()) * BLOCK, device="cuda")
         assert_close(out[mine], fo[rows], f"rank {rank} fine out")
@@ -112,8 +123,8 @@ def test_ring_steps_replayed_on_one_gpu(name, size, partition, metadata_group):
         owned = ids >= 0
         rows = (ids[owned, None] * BLOCK + torch.arange(BLOCK, device="cuda")).flatten()
         mine = torch.arange(int(owned.sum()) * BLOCK, device="cuda")
-        assert_close(dk_acc[rank][mine], fdk[rows], f"rank {rank} dk")
-        assert_close(dv_acc[rank][mine], fdv[rows], f"rank {rank} dv")
+        assert_close(dk_acc[rank][mine], fdk[rows], f"rank {rank} dk", peak_relative=True)
+        assert_close(dv_acc[rank][mine], fdv[rows], f"rank {rank} dv", peak_relative=True)
 
 
 def test_partial_merge_with_empty_steps():
@@ -157,7 +168,7 @@ def test_size_one_ring_group_matches_single_device():
             results.append((out, *torch.autograd.grad(out, leaves, dy)))
             vsa_core.check_status(layout)
         for tag, a, b in zip(("out", "dq", "dk", "dv", "dgate"), results[1], results[0]):
-            assert_close(a, b, f"size-one ring {tag}")
+            assert_close(a, b, f"size-one ring {tag}", peak_relative=tag in ("dk", "dv"))
     finally:
         dist.destroy_process_group()
 
@@ -169,4 +180,7 @@ def test_ring_over_nccl_matches_single_device():
            "--master-addr", "127.0.0.1", "--master-port", "29617", str(ROOT / "tests" / "ring_worker.py")]
     env = dict(os.environ, NCCL_NVLS_ENABLE="0")
     done = subprocess.run(cmd, capture_output=True, text=True, timeout=900, env=env)
+    log_dir = os.environ.get("VSA_TEST_LOG_DIR")
+    if log_dir:  # keep the workers' PARITY lines as evidence of the run
+        Path(log_dir, f"ring_worker_r{world}.log").write_text(done.stdout + done.stderr[-3000:])
     assert done.returncode == 0, done.stdout[-3000:] + done.stderr[-3000:]

@@ -31,7 +31,8 @@ def test_oracle_matches_reference_outputs_and_gradients(name, label):
         want = from_bits(CASES[f"{key}/{tag}"]).float()
         got = torch.zeros_like(q, dtype=torch.float32) if got is None else got
         # The reference's vectors are BF16 (and its gradients pass through BF16 intermediates).
-        assert_close(got[::stride], want, f"{name} {label} {tag}", max_abs=4e-2, rel_l2=1.2e-2)
+        assert_close(got[::stride], want, f"{name} {label} {tag}", max_abs=4e-2, rel_l2=1.2e-2,
+                     peak_relative=tag in ("dk", "dv"))
 
 
 @pytest.mark.parametrize("name", ["mixed", "ragged", "c1", "full_blocks", "partial_blocks"])

@@ -50,6 +50,27 @@ def test_static_scratch_routing_matches_vsa_route_on_two_calls_in_a_row():
         assert not torch.equal(got, layout.routing_indices)
 
 
+def test_static_scratch_call_leaves_device_memory_as_it_found_it():
+    """After the first call on the device (which may load the module that holds the array), a
+    call neither takes nor returns device memory: the driver's free-byte count and the bytes
+    held by this process's tensors are the same before and after."""
+    layout = build_vsa_layout(GEOMETRIES["c1"], head_num=2, device="cuda")
+    mean = _means(layout, 0)
+    first = _route_static(layout, mean)  # set-up call
+    plan = vsa_core.device_plan(layout)
+    index = layout.routing_indices.clone()
+    torch.cuda.synchronize()
+    free_before, held_before = torch.cuda.mem_get_info()[0], torch.cuda.memory_allocated()
+    for q_begin, q_end, kv_first, kv_last, keep, cursor in plan.spans:
+        _cabi.call("vsa_route_static", _cabi.ptr(mean[0]), _cabi.ptr(mean[1]), layout.head_num, q_begin, q_end,
+                   0, kv_first, kv_last, 0, keep, cursor, _cabi.ptr(index), index.stride(1), index.shape[-1],
+                   _cabi.stream(), launches=2)
+    torch.cuda.synchronize()
+    assert torch.cuda.mem_get_info()[0] == free_before
+    assert torch.cuda.memory_allocated() == held_before
+    assert torch.equal(index, first)
+
+
 def test_static_scratch_refuses_a_region_beyond_its_capacity():
     # 4096 x 2048 scores of one head need 32 MiB; the built-in array holds 16 MiB.
     mean = torch.zeros((4096, 1, 128), dtype=torch.float32, device="cuda")
