@@ -160,7 +160,7 @@ class CpuSample:
                           for x in self.slots[:2]]
         self.order = torch.randperm(layout.blocks, generator=torch.Generator().manual_seed(seed + 1))
 
-    def run(self, seconds, chunk=4):
+    def run(self, seconds, chunk=16):
         """One pass: returns (useful FLOPs done, seconds spent, query blocks done)."""
         layout, oracle = self.layout, self.oracle
         sizes = layout.block_sizes.double()
@@ -438,19 +438,16 @@ def main():
     # Each rank draws its own shard of the synthetic stream (same distribution as a sharded global tensor).
     if world > 1:
         gen.manual_seed(rank)
-    stacked = layers > 1
     leaves = [torch.randn(tokens, heads, DIM, device=device, dtype=torch.bfloat16, generator=gen).requires_grad_()
-              for _ in range(2 if stacked else 4)]
+              for _ in range(4)]
     dy = torch.randn(tokens, heads, DIM, device=device, dtype=torch.bfloat16,
                      generator=torch.Generator(device=device).manual_seed(1 + rank))
     scale = DIM ** -0.5
 
     def forward(xs):
-        if not stacked:
-            return vsa_attention(*xs, layout)
-        y, gate = xs
-        for _ in range(layers):  # one layout shared by the stack; q = k = v = the running activations
-            y = vsa_attention(y, y, y, gate, layout)
+        q, k, y, gate = xs
+        for _ in range(layers):  # a stack shares one layout; v of a layer = the previous layer's output
+            y = vsa_attention(q, k, y, gate, layout)
         return y
 
     def step():
@@ -483,9 +480,8 @@ def main():
     ms_per_step = elapsed.item() / args.steps
     vsa_core.check_status(layout)
 
-    # Useful FLOPs of this rank's queries from the routing table the step uses (first layer's
-    # inputs for a stack: the table depends on the activations, the count of listed blocks does not).
-    q0, k0 = leaves[0].detach(), (leaves[0] if stacked else leaves[1]).detach()
+    # Useful FLOPs of this rank's queries from the routing table the step uses.
+    q0, k0 = leaves[0].detach(), leaves[1].detach()
     index = vsa_ring.routing_table(q0, k0, layout) if world > 1 else vsa_core.routing_table(q0, k0, layout)
     flops = useful_flops(layout, index)
     total = torch.tensor([3 * layers * (flops["fine_forward"] + flops["coarse_forward"])], device=device,
@@ -519,7 +515,7 @@ def main():
     if rank == 0:
         result["breakdown_ms"] = {name: round(v["ms"], 3) for name, v in
                                   sorted(spans.items(), key=lambda kv: -kv[1]["ms"])}
-    if rank == 0 and world == 1 and not args.no_roofline and not stacked:
+    if rank == 0 and world == 1 and not args.no_roofline:
         kernels = kernel_rooflines(layout, leaves, scale, flops, peaks)
         name = max(kernels, key=lambda n: kernels[n]["ms"])
         top = kernels[name]

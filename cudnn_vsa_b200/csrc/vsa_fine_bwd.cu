@@ -21,30 +21,39 @@ namespace vsa {
 
 namespace {
 
-// Epilogue of a transposed accumulator: this thread owns head dim `col % 128`, its 64 columns are
-// the 64 slots of `block`.  Adds `term` and writes BF16 to the mapped rows of `out`, or FP32 in
-// slot order (added to the buffer's content when `accumulate`).  A warp store covers 32
-// consecutive elements of one row.
+// Epilogue of a transposed accumulator: this thread owns head dim `col % 128`, its columns are the
+// slots of `block`, of which the first `valid` are real and the first `computed` (a multiple of 16)
+// were produced by the products.  Adds `term` and writes BF16 to the mapped rows of `out`, or FP32
+// in slot order (added to the buffer's content when `accumulate`); padding slots are left alone.
+// A warp store covers 32 consecutive elements of one row.  The FP32 read-modify-write fetches a
+// whole chunk of old values before it stores any, so the loads are in flight together instead
+// of each waiting behind the previous store.
 VSA_DEVICE void store_grad_columns(bool have_acc, uint32_t tmem_addr, float term, const long long* out_rows,
                                    long long out_limit, __nv_bfloat16* out, float* out_f32, bool accumulate,
-                                   long long block, long long width, long long col) {
+                                   long long block, long long width, long long col, int valid, int computed) {
 #pragma unroll
   for (int c = 0; c < 2; ++c) {
+    if (c * 32 >= valid) break;
     uint32_t bits[32] = {};
-    if (have_acc) {
+    if (have_acc && c * 32 < computed) {
       VSA_TMEM_LD_32x32b_X32(bits, tmem_addr + c * 32);
       tmem_wait_ld();
     }
+    if (out_f32 != nullptr) {
+      float* base = out_f32 + (block * kBlock + c * 32) * width + col;
+      float old[32];
 #pragma unroll
-    for (int i = 0; i < 32; ++i) {
-      const int r = c * 32 + i;
-      const float value = __uint_as_float(bits[i]) + term;
-      if (out_f32 != nullptr) {
-        float* dst = out_f32 + (block * kBlock + r) * width + col;
-        *dst = accumulate ? *dst + value : value;
-      } else {
+      for (int i = 0; i < 32; ++i) old[i] = (accumulate && c * 32 + i < valid) ? base[i * width] : 0.f;
+#pragma unroll
+      for (int i = 0; i < 32; ++i)
+        if (c * 32 + i < valid) base[i * width] = old[i] + (__uint_as_float(bits[i]) + term);
+    } else {
+#pragma unroll
+      for (int i = 0; i < 32; ++i) {
+        const int r = c * 32 + i;
         const long long row = out_rows[r];
-        if (row >= 0 && row < out_limit) out[row * width + col] = __float2bfloat16(value);
+        if (r < valid && row >= 0 && row < out_limit)
+          out[row * width + col] = __float2bfloat16(__uint_as_float(bits[i]) + term);
       }
     }
   }
@@ -93,26 +102,49 @@ struct MaskCursor {
   }
 };
 
-// S or dP = A B^T: A = a K-major pair stage (128 query rows), B = the K-major K or V tile; eight
-// K=16 steps over the two 64-wide dim halves.
-VSA_DEVICE void issue_pair_scores(uint32_t tmem_d, uint32_t pair_lo, uint32_t tile_lo) {
-  constexpr uint32_t idesc = umma_idesc(128, 64, 0, 0);
+// S or dP = A B^T: A = a K-major pair stage (128 query rows), B = the first N rows of the K-major
+// K or V tile (N = the block's valid keys rounded up to 16, carried by `idesc`); eight K=16
+// steps over the two 64-wide dim halves.
+VSA_DEVICE void issue_pair_scores(uint32_t tmem_d, uint32_t pair_lo, uint32_t tile_lo, uint32_t idesc) {
 #pragma unroll
   for (int ks = 0; ks < 8; ++ks)
     umma_ss_lo(tmem_d, pair_lo + (ks >> 2) * (kTileBytes >> 4) + (ks & 3) * 2,
                tile_lo + (ks >> 2) * (kHalfTileBytes >> 4) + (ks & 3) * 2, idesc, ks > 0);
 }
 
-// D^T[128 dims x 64 keys] (+)= A^T B over the query rows of one or two blocks: A = a pair stage
-// read MN-major (16 rows = 2 KiB per step, dim halves 16 KiB apart), B = P or dS rows
-// [query][key] read MN-major.
-VSA_DEVICE void issue_pair_grad(uint32_t tmem_d, uint32_t a_mn_lo, uint32_t b_lo, bool two, bool accumulate) {
-  constexpr uint32_t idesc = umma_idesc(128, 64, 1, 1);
+// D^T[128 dims x N keys] (+)= A^T B over the query rows of one or two blocks: A = a pair stage
+// read MN-major (16 rows = 2 KiB per step, dim halves 16 KiB apart), B = the first N keys of the
+// P or dS rows [query][key] read MN-major.
+VSA_DEVICE void issue_pair_grad(uint32_t tmem_d, uint32_t a_mn_lo, uint32_t b_lo, bool two, bool accumulate,
+                                uint32_t idesc) {
 #pragma unroll
   for (int ks = 0; ks < 4; ++ks) umma_ss_lo(tmem_d, a_mn_lo + ks * 128, b_lo + ks * 128, idesc, accumulate || ks > 0);
   if (two) {
 #pragma unroll
     for (int ks = 4; ks < 8; ++ks) umma_ss_lo(tmem_d, a_mn_lo + ks * 128, b_lo + ks * 128, idesc, 1u);
+  }
+}
+
+// P and dS of 32 keys of this thread's query row from the S and dP accumulator bits.  kMasked: the
+// chunk holds keys at or beyond `kv_size` (padding, or columns the products never wrote), which
+// need a select per element; a chunk of valid keys skips it - the math loop is bound by
+// instruction issue.  Selects, not products: rows of an absent query block and masked columns may
+// hold anything.
+template <bool kMasked>
+VSA_DEVICE void pds_chunk(const uint32_t (&s_bits)[32], const uint32_t (&dp_bits)[32], bool live, int first_key,
+                          int kv_size, float sl2, float neg_lse2, float delta, float scale, uint32_t (&p_packed)[16],
+                          uint32_t (&ds_packed)[16]) {
+#pragma unroll
+  for (int e = 0; e < 32; e += 2) {
+    float pr[2], ds[2];
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {
+      const bool on = kMasked ? (live && first_key + e + u < kv_size) : live;
+      pr[u] = on ? fast_exp2(fmaf(__uint_as_float(s_bits[e + u]), sl2, neg_lse2)) : 0.f;
+      ds[u] = on ? pr[u] * (__uint_as_float(dp_bits[e + u]) - delta) * scale : 0.f;
+    }
+    p_packed[e >> 1] = pack_bf16(pr[0], pr[1]);
+    ds_packed[e >> 1] = pack_bf16(ds[0], ds[1]);
   }
 }
 
@@ -175,6 +207,10 @@ __global__ void __launch_bounds__(kDkvThreads, 1) fine_bwd_dkv_kernel(const __gr
   volatile int* abort_flag = &sm.abort_flag;
   MaskCursor cursor(mask, p.mask_words);
   const int kv_size = p.kv_sizes != nullptr ? p.kv_sizes[kvb] : kBlock;
+  // Keys the products cover: the block's valid keys rounded up to the MMA's N granularity.  A
+  // short block (an edge tile of 8, 12, 16 ... keys) runs every product with a narrow N, moves a
+  // fraction of the P / dS bytes and does a fraction of the exponentials.
+  const int kv_n = kv_size >= kBlock ? kBlock : (kv_size <= 16 ? 16 : ((kv_size + 15) & ~15));
 
   // Barrier discipline: a barrier is only ever waited on for its NEWEST commit or arrival round;
   // every barrier belongs to one buffer (stage = warpgroup = pair parity) and the round after the
@@ -215,17 +251,18 @@ __global__ void __launch_bounds__(kDkvThreads, 1) fine_bwd_dkv_kernel(const __gr
       const uint32_t k_lo = umma_desc_lo(smem_u32(sm.k), 16), v_lo = umma_desc_lo(smem_u32(sm.v), 16);
       const uint32_t q_lo0 = umma_desc_lo(smem_u32(sm.q[0]), 16), do_lo0 = umma_desc_lo(smem_u32(sm.d_o[0]), 16);
       constexpr uint32_t kPairLo = kPairBytes >> 4;
+      const uint32_t idesc = umma_idesc(128, kv_n, 0, 0);
       mbar_wait(&sm.kv_full, 0, abort_flag, p.status, 21);
       for (int j = 0; j < pairs; ++j) {
         const int b = j & 1;
         if (j >= 2) mbar_wait(&sm.sp_free[b], ((j >> 1) - 1) & 1, abort_flag, p.status, 28);
         mbar_wait(&sm.q_full[b], (j >> 1) & 1, abort_flag, p.status, 26);
         tc_fence_after();
-        if (leader) issue_pair_scores(tmem + b * 128, q_lo0 + b * kPairLo, k_lo);
+        if (leader) issue_pair_scores(tmem + b * 128, q_lo0 + b * kPairLo, k_lo, idesc);
         mbar_wait(&sm.do_full[b], (j >> 1) & 1, abort_flag, p.status, 30);
         tc_fence_after();
         if (leader) {
-          issue_pair_scores(tmem + b * 128 + 64, do_lo0 + b * kPairLo, v_lo);
+          issue_pair_scores(tmem + b * 128 + 64, do_lo0 + b * kPairLo, v_lo, idesc);
           umma_commit(&sm.sp_done[b]);
         }
       }
@@ -239,15 +276,16 @@ __global__ void __launch_bounds__(kDkvThreads, 1) fine_bwd_dkv_kernel(const __gr
       const uint32_t pt_lo0 = umma_desc_lo(smem_u32(sm.pt[0]), kHalfTileBytes);
       const uint32_t dst_lo0 = umma_desc_lo(smem_u32(sm.dst[0]), kHalfTileBytes);
       constexpr uint32_t kPairLo = kPairBytes >> 4, kBufLo = kTileBytes >> 4;
+      const uint32_t idesc = umma_idesc(128, kv_n, 1, 1);
       for (int j = 0; j < pairs; ++j) {
         const int b = j & 1;
         mbar_wait(&sm.pd_ready[b], (j >> 1) & 1, abort_flag, p.status, 29);
         tc_fence_after();
         const bool two = 2 * j + 1 < n;
         if (leader) {
-          issue_pair_grad(tmem + kColDk, q_mn_lo0 + b * kPairLo, dst_lo0 + b * kBufLo, two, j > 0);  // dK^T += Q^T dS
+          issue_pair_grad(tmem + kColDk, q_mn_lo0 + b * kPairLo, dst_lo0 + b * kBufLo, two, j > 0, idesc);  // dK^T += Q^T dS
           umma_commit(&sm.q_free[b]);
-          issue_pair_grad(tmem + kColDv, do_mn_lo0 + b * kPairLo, pt_lo0 + b * kBufLo, two, j > 0);  // dV^T += dO^T P
+          issue_pair_grad(tmem + kColDv, do_mn_lo0 + b * kPairLo, pt_lo0 + b * kBufLo, two, j > 0, idesc);  // dV^T += dO^T P
           umma_commit(&sm.do_free[b]);
           umma_commit(&sm.pd_free[b]);
         }
@@ -292,33 +330,26 @@ __global__ void __launch_bounds__(kDkvThreads, 1) fine_bwd_dkv_kernel(const __gr
       tc_fence_after();
 #pragma unroll
       for (int c = 0; c < 2; ++c) {
+        if (c * 32 >= kv_n) break;  // a short KV block has no second half
         uint32_t s_bits[32], dp_bits[32];
         VSA_TMEM_LD_32x32b_X32(s_bits, tmem_s + c * 32);
         VSA_TMEM_LD_32x32b_X32(dp_bits, tmem_s + 64 + c * 32);
         tmem_wait_ld();
-        if (c == 1) {
-          // Both halves of S and dP are in registers: the accumulators may be overwritten.
+        if ((c + 1) * 32 >= kv_n) {
+          // All of S and dP is in registers: the accumulators may be overwritten.
           tc_fence_before();
           mbar_arrive(&sm.sp_free[group]);
         }
         uint32_t p_packed[16], ds_packed[16];
-#pragma unroll
-        for (int e = 0; e < 32; e += 2) {
-          float pr[2], ds[2];
-#pragma unroll
-          for (int u = 0; u < 2; ++u) {
-            // Selects, not products: rows of an absent query block and padded keys may hold anything.
-            const bool on = live && (c * 32 + e + u < kv_size);
-            pr[u] = on ? fast_exp2(fmaf(__uint_as_float(s_bits[e + u]), sl2, neg_lse2)) : 0.f;
-            ds[u] = on ? pr[u] * (__uint_as_float(dp_bits[e + u]) - delta) * scale : 0.f;
-          }
-          p_packed[e >> 1] = pack_bf16(pr[0], pr[1]);
-          ds_packed[e >> 1] = pack_bf16(ds[0], ds[1]);
-        }
+        if ((c + 1) * 32 <= kv_size)
+          pds_chunk<false>(s_bits, dp_bits, live, c * 32, kv_size, sl2, neg_lse2, delta, scale, p_packed, ds_packed);
+        else
+          pds_chunk<true>(s_bits, dp_bits, live, c * 32, kv_size, sl2, neg_lse2, delta, scale, p_packed, ds_packed);
         // The gradient products of this warpgroup's previous pair have finished reading P / dS.
         if (c == 0 && i >= 2) mbar_wait(&sm.pd_free[group], ((i >> 1) - 1) & 1, abort_flag, p.status, 24);
 #pragma unroll
         for (int v4 = 0; v4 < 4; ++v4) {
+          if ((c * 4 + v4) * 8 >= kv_n) break;  // the products read kv_n keys of every row
           const uint32_t off = static_cast<uint32_t>(((c * 4 + v4) ^ (qrow & 7)) << 4);
           *reinterpret_cast<uint4*>(p_row + off) =
               make_uint4(p_packed[4 * v4], p_packed[4 * v4 + 1], p_packed[4 * v4 + 2], p_packed[4 * v4 + 3]);
@@ -344,11 +375,11 @@ __global__ void __launch_bounds__(kDkvThreads, 1) fine_bwd_dkv_kernel(const __gr
     if (group == 0) {
       const float term = pool_term(p.dk_pool, p.pool_f32, p.kv_block_coarse, kvb, kv_size, width, col);
       store_grad_columns(n > 0, tmem + lane_base + kColDk, term, sm.out_row, p.kv_out_rows, p.dk, p.dk_f32,
-                         p.f32_accumulate != 0, kvb, width, col);
+                         p.f32_accumulate != 0, kvb, width, col, kv_size, kv_n);
     } else {
       const float term = pool_term(p.dv_pool, p.pool_f32, p.kv_block_coarse, kvb, kv_size, width, col);
       store_grad_columns(n > 0, tmem + lane_base + kColDv, term, sm.out_row, p.kv_out_rows, p.dv, p.dv_f32,
-                         p.f32_accumulate != 0, kvb, width, col);
+                         p.f32_accumulate != 0, kvb, width, col, kv_size, kv_n);
     }
   }
   tc_fence_before();

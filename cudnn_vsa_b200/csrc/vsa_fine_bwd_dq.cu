@@ -50,10 +50,10 @@ struct DqSmem {  // placed at a 1024-byte aligned address; every tile offset is 
   int abort_flag;
 };
 
-// S^T or dP^T = A B^T: A = a K-major pair stage (128 rows), B = a K-major 64-row tile; eight
+// S^T or dP^T = A B^T: A = a K-major pair stage (128 rows), B = the first N rows of a K-major
+// 64-row tile (N = the query block's valid rows rounded up to 16, carried by `idesc`); eight
 // K=16 steps over the two 64-wide dim halves.
-VSA_DEVICE void issue_scores(uint32_t tmem_d, uint32_t pair_lo, uint32_t tile_lo) {
-  constexpr uint32_t idesc = umma_idesc(128, 64, 0, 0);
+VSA_DEVICE void issue_scores(uint32_t tmem_d, uint32_t pair_lo, uint32_t tile_lo, uint32_t idesc) {
 #pragma unroll
   for (int ks = 0; ks < 8; ++ks)
     umma_ss_lo(tmem_d, pair_lo + (ks >> 2) * (kTileBytes >> 4) + (ks & 3) * 2,
@@ -61,14 +61,52 @@ VSA_DEVICE void issue_scores(uint32_t tmem_d, uint32_t pair_lo, uint32_t tile_lo
 }
 
 // dQ^T (+)= K^T dS^T over the keys of one or two blocks: A = the K pair read MN-major (16 keys =
-// 2 KiB per step, dim halves 16 KiB apart), B = dS^T rows [key][query] read MN-major.
-VSA_DEVICE void issue_dq(uint32_t tmem_d, uint32_t k_mn_lo, uint32_t ds_lo, bool two, bool accumulate) {
-  constexpr uint32_t idesc = umma_idesc(128, 64, 1, 1);
+// 2 KiB per step, dim halves 16 KiB apart), B = the first N queries of the dS^T rows [key][query]
+// read MN-major.  `steps0` / `steps1`: K=16 steps that hold real keys of the first / second
+// block (0 = block absent); dS^T is zero on padded keys, so their steps are not issued.  Full
+// blocks take the straight-line path: the issuing thread pays for every instruction between MMAs.
+VSA_DEVICE void issue_dq(uint32_t tmem_d, uint32_t k_mn_lo, uint32_t ds_lo, int steps0, int steps1, bool accumulate,
+                         uint32_t idesc) {
+  if (steps0 == 4 && (steps1 == 4 || steps1 == 0)) {
 #pragma unroll
-  for (int ks = 0; ks < 4; ++ks) umma_ss_lo(tmem_d, k_mn_lo + ks * 128, ds_lo + ks * 128, idesc, accumulate || ks > 0);
-  if (two) {
+    for (int ks = 0; ks < 4; ++ks) umma_ss_lo(tmem_d, k_mn_lo + ks * 128, ds_lo + ks * 128, idesc, accumulate || ks > 0);
+    if (steps1) {
 #pragma unroll
-    for (int ks = 4; ks < 8; ++ks) umma_ss_lo(tmem_d, k_mn_lo + ks * 128, ds_lo + ks * 128, idesc, 1u);
+      for (int ks = 4; ks < 8; ++ks) umma_ss_lo(tmem_d, k_mn_lo + ks * 128, ds_lo + ks * 128, idesc, 1u);
+    }
+    return;
+  }
+#pragma unroll
+  for (int ks = 0; ks < 4; ++ks)
+    if (ks < steps0) umma_ss_lo(tmem_d, k_mn_lo + ks * 128, ds_lo + ks * 128, idesc, accumulate || ks > 0);
+#pragma unroll
+  for (int ks = 0; ks < 4; ++ks)
+    if (ks < steps1) umma_ss_lo(tmem_d, k_mn_lo + (4 + ks) * 128, ds_lo + (4 + ks) * 128, idesc, 1u);
+}
+
+// dS^T of 32 queries of this thread's key from the S^T and dP^T accumulator bits.  kMasked: the
+// chunk holds query columns at or beyond `q_n` that the products never wrote and that must come
+// out as zero; a full chunk skips the per-element compare (the loop is bound by instruction
+// issue).  A query row without keys has neg_lse2 = -inf: exp2(-inf) = 0.
+template <bool kMasked>
+VSA_DEVICE void ds_chunk(const uint32_t (&s_bits)[32], const uint32_t (&dp_bits)[32], bool live, int first_query,
+                         int q_n, const float* neg_lse2, const float* delta, float sl2, float scale,
+                         uint32_t* packed) {
+#pragma unroll
+  for (int e = 0; e < 32; e += 4) {
+    const float4 nl = *reinterpret_cast<const float4*>(neg_lse2 + first_query + e);
+    const float4 dl = *reinterpret_cast<const float4*>(delta + first_query + e);
+    const float nls[4] = {nl.x, nl.y, nl.z, nl.w}, dls[4] = {dl.x, dl.y, dl.z, dl.w};
+    float ds[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const float pr = fast_exp2(fmaf(__uint_as_float(s_bits[e + u]), sl2, nls[u]));
+      const float v = pr * (__uint_as_float(dp_bits[e + u]) - dls[u]) * scale;
+      // A select: rows of an absent or padded key and unwritten columns may hold anything.
+      ds[u] = (kMasked ? (live && first_query + e + u < q_n) : live) ? v : 0.f;
+    }
+    packed[e >> 1] = pack_bf16(ds[0], ds[1]);
+    packed[(e >> 1) + 1] = pack_bf16(ds[2], ds[3]);
   }
 }
 
@@ -84,6 +122,9 @@ __global__ void __launch_bounds__(kThreads, 1) fine_bwd_dq_kernel(const __grid_c
   const int n = p.counts[static_cast<long long>(head) * p.count_head_stride + qb];
   const int32_t* list = p.indices + static_cast<long long>(head) * p.index_head_stride +
                         static_cast<long long>(qb) * p.capacity;
+  // Query rows the products cover: the block's valid rows rounded up to the MMA's N granularity.
+  const int q_size = p.q_sizes != nullptr ? p.q_sizes[qb] : kBlock;
+  const int q_n = q_size >= kBlock ? kBlock : (q_size <= 16 ? 16 : ((q_size + 15) & ~15));
 
   if (tid == 0) {
     mbar_init(&sm.qdo_full, 1);
@@ -176,16 +217,17 @@ __global__ void __launch_bounds__(kThreads, 1) fine_bwd_dq_kernel(const __grid_c
       constexpr uint32_t kPairLo = kPairBytes >> 4;
       int s_k = 0, s_v = 0;                   // stages of the next score products
       uint32_t s_k_phase = 0, s_v_phase = 0;  // parities of those stages' current fills
+      const uint32_t idesc = umma_idesc(128, q_n, 0, 0);
       mbar_wait(&sm.qdo_full, 0, abort_flag, p.status, 11);
       for (int j = 0; j < pairs; ++j) {
         if (j >= 2) mbar_wait(&sm.sp_free[j & 1], ((j >> 1) - 1) & 1, abort_flag, p.status, 17);
         mbar_wait(&sm.k_full[s_k], s_k_phase, abort_flag, p.status, 15);
         tc_fence_after();
-        if (leader) issue_scores(tmem + (j & 1) * 128, k_lo0 + s_k * kPairLo, q_lo);
+        if (leader) issue_scores(tmem + (j & 1) * 128, k_lo0 + s_k * kPairLo, q_lo, idesc);
         mbar_wait(&sm.v_full[s_v], s_v_phase, abort_flag, p.status, 19);
         tc_fence_after();
         if (leader) {
-          issue_scores(tmem + (j & 1) * 128 + 64, v_lo0 + s_v * kPairLo, do_lo);
+          issue_scores(tmem + (j & 1) * 128 + 64, v_lo0 + s_v * kPairLo, do_lo, idesc);
           umma_commit(&sm.sp_done[j & 1]);
           umma_commit(&sm.v_free[s_v]);
         }
@@ -207,11 +249,27 @@ __global__ void __launch_bounds__(kThreads, 1) fine_bwd_dq_kernel(const __grid_c
       const uint32_t ds_lo0 = umma_desc_lo(smem_u32(sm.ds[0]), kHalfTileBytes);
       constexpr uint32_t kPairLo = kPairBytes >> 4, kDsLo = kTileBytes >> 4;
       int d_k = 0;  // K stage of the next dQ product
+      const uint32_t idesc = umma_idesc(128, q_n, 1, 1);
+      // K=16 steps that hold real keys, per block of the pair; looked up one pair ahead so the
+      // two dependent loads never sit between a completed wait and its products.
+      auto steps_of = [&](int i, int& s0, int& s1) {
+        s0 = 4;
+        s1 = (2 * i + 1 < n) ? 4 : 0;
+        if (p.kv_sizes != nullptr) {
+          s0 = (p.kv_sizes[list[2 * i]] + 15) >> 4;
+          s0 = s0 < 1 ? 1 : s0;
+          if (s1) s1 = (p.kv_sizes[list[2 * i + 1]] + 15) >> 4;
+        }
+      };
+      int steps0 = 4, steps1 = 0;
+      steps_of(0, steps0, steps1);
       for (int i = 0; i < pairs; ++i) {
+        const int now0 = steps0, now1 = steps1;
+        if (i + 1 < pairs) steps_of(i + 1, steps0, steps1);
         mbar_wait(&sm.ds_ready[i & 1], (i >> 1) & 1, abort_flag, p.status, 18);
         tc_fence_after();
         if (leader) {
-          issue_dq(tmem + kColDq, k_mn_lo0 + d_k * kPairLo, ds_lo0 + (i & 1) * kDsLo, 2 * i + 1 < n, i > 0);
+          issue_dq(tmem + kColDq, k_mn_lo0 + d_k * kPairLo, ds_lo0 + (i & 1) * kDsLo, now0, now1, i > 0, idesc);
           umma_commit(&sm.k_free[d_k]);
           umma_commit(&sm.ds_free[i & 1]);
         }
@@ -243,38 +301,29 @@ __global__ void __launch_bounds__(kThreads, 1) fine_bwd_dq_kernel(const __grid_c
       uint32_t packed[32];
 #pragma unroll
       for (int c = 0; c < 2; ++c) {
+        if (c * 32 >= q_n) break;  // a short query block has no second half
         uint32_t s_bits[32], dp_bits[32];
         VSA_TMEM_LD_32x32b_X32(s_bits, tmem_s + c * 32);
         VSA_TMEM_LD_32x32b_X32(dp_bits, tmem_s + 64 + c * 32);
         tmem_wait_ld();
-        if (c == 1) {
-          // Both halves of S^T and dP^T are in registers: the accumulators may be overwritten.
+        if ((c + 1) * 32 >= q_n) {
+          // All of S^T and dP^T is in registers: the accumulators may be overwritten.
           tc_fence_before();
           mbar_arrive(&sm.sp_free[group]);
         }
-#pragma unroll
-        for (int e = 0; e < 32; e += 4) {
-          const float4 nl = *reinterpret_cast<const float4*>(&sm.neg_lse2[c * 32 + e]);
-          const float4 dl = *reinterpret_cast<const float4*>(&sm.delta[c * 32 + e]);
-          const float nls[4] = {nl.x, nl.y, nl.z, nl.w}, dls[4] = {dl.x, dl.y, dl.z, dl.w};
-          float ds[4];
-#pragma unroll
-          for (int u = 0; u < 4; ++u) {
-            // A query row without keys has neg_lse2 = -inf: exp2(-inf) = 0.
-            const float pr = fast_exp2(fmaf(__uint_as_float(s_bits[e + u]), sl2, nls[u]));
-            const float v = pr * (__uint_as_float(dp_bits[e + u]) - dls[u]) * scale;
-            ds[u] = live ? v : 0.f;  // a select: rows of an absent or padded key may hold anything
-          }
-          packed[c * 16 + (e >> 1)] = pack_bf16(ds[0], ds[1]);
-          packed[c * 16 + (e >> 1) + 1] = pack_bf16(ds[2], ds[3]);
-        }
+        if ((c + 1) * 32 <= q_n)
+          ds_chunk<false>(s_bits, dp_bits, live, c * 32, q_n, sm.neg_lse2, sm.delta, sl2, scale, packed + c * 16);
+        else
+          ds_chunk<true>(s_bits, dp_bits, live, c * 32, q_n, sm.neg_lse2, sm.delta, sl2, scale, packed + c * 16);
       }
       // The dQ product of this warpgroup's previous pair has finished reading the dS^T buffer.
       if (i >= 2) mbar_wait(&sm.ds_free[group], ((i >> 1) - 1) & 1, abort_flag, p.status, 14);
 #pragma unroll
-      for (int c = 0; c < 8; ++c)
+      for (int c = 0; c < 8; ++c) {
+        if (c * 8 >= q_n) break;  // the product reads q_n queries of every row
         *reinterpret_cast<uint4*>(ds_row + ((c ^ (key & 7)) << 4)) =
             make_uint4(packed[4 * c], packed[4 * c + 1], packed[4 * c + 2], packed[4 * c + 3]);
+      }
       fence_proxy_async_smem();
       tc_fence_before();
       mbar_arrive(&sm.ds_ready[group]);
@@ -287,27 +336,35 @@ __global__ void __launch_bounds__(kThreads, 1) fine_bwd_dq_kernel(const __grid_c
       mbar_wait(&sm.dq_final, 0, abort_flag, p.status, 16);
       tc_fence_after();
     }
-    // Thread = head dim `key`; warpgroup g takes query rows [32g, 32g+32).  A warp store covers
-    // 32 consecutive elements of one row.
+    // Thread = head dim `key`; warpgroup g takes query rows [32g, 32g+32), of which only the
+    // block's valid rows are written.  A warp store covers 32 consecutive elements of one row.
     const long long width = static_cast<long long>(p.heads) * kDim;
     const long long col = static_cast<long long>(head) * kDim + key;
-    const int q_size = p.q_sizes != nullptr ? p.q_sizes[qb] : kBlock;
-    const float term = pool_term(p.dq_pool, p.pool_f32, p.q_block_coarse, qb, q_size, width, col);
-    uint32_t bits[32] = {};
-    if (n > 0) {
-      VSA_TMEM_LD_32x32b_X32(bits, tmem + lane_base + kColDq + group * 32);
-      tmem_wait_ld();
-    }
-#pragma unroll
-    for (int i = 0; i < 32; ++i) {
-      const int r = group * 32 + i;
-      const float value = __uint_as_float(bits[i]) + term;
+    if (group * 32 < q_size) {
+      const float term = pool_term(p.dq_pool, p.pool_f32, p.q_block_coarse, qb, q_size, width, col);
+      uint32_t bits[32] = {};
+      if (n > 0) {
+        VSA_TMEM_LD_32x32b_X32(bits, tmem + lane_base + kColDq + group * 32);
+        tmem_wait_ld();
+      }
       if (p.dq_f32 != nullptr) {
-        float* dst = p.dq_f32 + (static_cast<long long>(qb) * kBlock + r) * width + col;
-        *dst = p.f32_accumulate ? *dst + value : value;
+        // Running FP32 dQ of the ring: every old value of the chunk is fetched before the first
+        // store, so the loads are in flight together.
+        float* base = p.dq_f32 + (static_cast<long long>(qb) * kBlock + group * 32) * width + col;
+        float old[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) old[i] = (p.f32_accumulate && group * 32 + i < q_size) ? base[i * width] : 0.f;
+#pragma unroll
+        for (int i = 0; i < 32; ++i)
+          if (group * 32 + i < q_size) base[i * width] = old[i] + (__uint_as_float(bits[i]) + term);
       } else {
-        const long long row = sm.out_row[r];
-        if (row >= 0 && row < p.q_out_rows) p.dq[row * width + col] = __float2bfloat16(value);
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          const int r = group * 32 + i;
+          const long long row = sm.out_row[r];
+          if (r < q_size && row >= 0 && row < p.q_out_rows)
+            p.dq[row * width + col] = __float2bfloat16(__uint_as_float(bits[i]) + term);
+        }
       }
     }
   }

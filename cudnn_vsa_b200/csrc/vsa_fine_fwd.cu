@@ -81,16 +81,29 @@ VSA_DEVICE void issue_qk(uint32_t tmem_s, uint32_t q_lo, uint32_t k_lo, bool two
 }
 
 // O (+)= P V.  A = P in tensor memory (8 columns per 16 keys); B = V tile [key][dim] read
-// MN-major (two 64-wide dim halves 8 KiB apart, 16 keys = 2 KiB per K step).
-VSA_DEVICE void issue_pv(uint32_t tmem_o, uint32_t tmem_p, uint32_t v_lo, bool two, bool accumulate) {
+// MN-major (two 64-wide dim halves 8 KiB apart, 16 keys = 2 KiB per K step).  Only the K=16
+// steps that hold valid keys are issued (`steps0` of the first block, `steps1` of the second,
+// 0 = block absent): P is zero on masked keys.
+VSA_DEVICE void issue_pv(uint32_t tmem_o, uint32_t tmem_p, uint32_t v_lo, int steps0, int steps1, bool accumulate) {
   constexpr uint32_t idesc = umma_idesc(64, 128, 0, 1);
+  if (steps0 == 4 && (steps1 == 4 || steps1 == 0)) {
+    // Full blocks: straight-line issue, nothing between the MMAs.
 #pragma unroll
-  for (int ks = 0; ks < 4; ++ks) umma_ts_lo(tmem_o, tmem_p + ks * 8, v_lo + ks * (2048 >> 4), idesc, accumulate || ks > 0);
-  if (two) {
+    for (int ks = 0; ks < 4; ++ks) umma_ts_lo(tmem_o, tmem_p + ks * 8, v_lo + ks * (2048 >> 4), idesc, accumulate || ks > 0);
+    if (steps1) {
 #pragma unroll
-    for (int ks = 0; ks < 4; ++ks)
-      umma_ts_lo(tmem_o, tmem_p + (4 + ks) * 8, v_lo + (kTileBytes >> 4) + ks * (2048 >> 4), idesc, 1u);
+      for (int ks = 0; ks < 4; ++ks)
+        umma_ts_lo(tmem_o, tmem_p + (4 + ks) * 8, v_lo + (kTileBytes >> 4) + ks * (2048 >> 4), idesc, 1u);
+    }
+    return;
   }
+#pragma unroll
+  for (int ks = 0; ks < 4; ++ks)
+    if (ks < steps0) umma_ts_lo(tmem_o, tmem_p + ks * 8, v_lo + ks * (2048 >> 4), idesc, accumulate || ks > 0);
+#pragma unroll
+  for (int ks = 0; ks < 4; ++ks)
+    if (ks < steps1)
+      umma_ts_lo(tmem_o, tmem_p + (4 + ks) * 8, v_lo + (kTileBytes >> 4) + ks * (2048 >> 4), idesc, 1u);
 }
 
 }  // namespace
@@ -239,8 +252,12 @@ __global__ void __launch_bounds__(kThreads, 1) fine_fwd_kernel(const __grid_cons
         mbar_wait(&sm.p_ready[stage], phase, abort_flag, p.status, 9);
         mbar_wait(&sm.v_full[stage], phase, abort_flag, p.status, 6);
         tc_fence_after();
+        // Valid keys of the pair's blocks (written by the K producer with the stage; the softmax
+        // that just finished read the same slot).  The first block always gets one step.
+        const int size0 = sm.kv_size[i % (2 * kStages)][0], size1 = sm.kv_size[i % (2 * kStages)][1];
+        const int steps0 = size0 <= 16 ? 1 : (size0 + 15) >> 4, steps1 = (size1 + 15) >> 4;
         if (leader) {
-          issue_pv(tmem + kColO, tmem + stage * 128, v_lo0 + stage * kStageLo, 2 * i + 1 < n, i > 0);
+          issue_pv(tmem + kColO, tmem + stage * 128, v_lo0 + stage * kStageLo, steps0, steps1, i > 0);
           umma_commit(&sm.o_done[i & 1]);
           umma_commit(&sm.v_free[stage]);
           umma_commit(&sm.p_free[stage]);

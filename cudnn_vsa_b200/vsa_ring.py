@@ -149,6 +149,13 @@ def _bwd_call(q, k, v, d_o, index, counts, sizes_q, sizes_kv, scale, lse, delta,
               dq=None, dk=None, dv=None, dq_f32=None, dk_f32=None, dv_f32=None, accumulate=0):
     heads = q.shape[1]
     q_blocks, kv_blocks = q.shape[0] // BLOCK, k.shape[0] // BLOCK
+    with _cabi.mark("ring_step_dq" if parts & 2 else "ring_step_dkv"):
+        _bwd_launch(q, k, v, d_o, index, counts, sizes_q, sizes_kv, scale, lse, delta, mask, status, parts, dq, dk,
+                    dv, dq_f32, dk_f32, dv_f32, accumulate, heads, q_blocks, kv_blocks)
+
+
+def _bwd_launch(q, k, v, d_o, index, counts, sizes_q, sizes_kv, scale, lse, delta, mask, status, parts, dq, dk, dv,
+                dq_f32, dk_f32, dv_f32, accumulate, heads, q_blocks, kv_blocks):
     _cabi.call("vsa_fine_bwd", _p(q), _p(k), _p(v), _p(d_o), q_blocks, kv_blocks, heads, _p(index), _p(counts),
                index.stride(0), counts.stride(0), index.shape[-1], _p(sizes_q), _p(sizes_kv), scale, _p(lse),
                _p(delta), _p(mask), _p(dq), _p(dk), _p(dv), q.shape[0], k.shape[0], None, None, None, None, None,

@@ -87,26 +87,33 @@ def test_block_order_stack_h24_eight_layers_one_layout():
     assert torch.equal(block_wo_padding_to_raster(position_b, vsa_layout=layout), position)
     del hidden, hidden_b
     # Eight stacked calls through one layout on block-ordered activations, gradients through all.
-    x = _inputs(tokens, heads, 1, seed=3)[0].requires_grad_()
-    gate = torch.full_like(x, 0.5)
-    y, last_input = x, None
-    for layer in range(layers):
-        last_input = y
-        y = vsa_attention(y, y, y, gate, layout)
+    # Layer l attends with seeded normal q, k and gate (seed l) over v = the running activations,
+    # so every layer sees well-conditioned scores and the gradient reaches the first input.
+    def layer_inputs(layer, lay):
+        return [raster_to_block_wo_padding(t, vsa_layout=lay) if lay is layout else t
+                for t in _inputs(tokens, heads, 3, seed=layer)]
+
+    def stack(x0, lay):
+        y, last = x0, None
+        for layer in range(layers):
+            q, k, gate = layer_inputs(layer, lay)
+            last = (q, k, y, gate)
+            y = vsa_attention(q, k, y, gate, lay)
+        return y, last
+
+    x_raster = _inputs(tokens, heads, 1, seed=30)[0]
+    x = raster_to_block_wo_padding(x_raster, vsa_layout=layout).requires_grad_()
+    y, last = stack(x, layout)
     grad, = torch.autograd.grad(y, x, torch.ones_like(y))
-    assert torch.isfinite(y).all() and torch.isfinite(grad).all()
+    assert torch.isfinite(y).all() and torch.isfinite(grad).all() and grad.count_nonzero()
     vsa_core.check_status(layout)
     # The same stack in raster order gives the same result after reordering.
     raster_layout = build_vsa_layout(GEOMETRIES["c4"], head_num=heads, device="cuda")
     with torch.no_grad():
-        yr = block_wo_padding_to_raster(x.detach(), vsa_layout=layout)
-        gate_r = torch.full_like(yr, 0.5)
-        for layer in range(layers):
-            yr = vsa_attention(yr, yr, yr, gate_r, raster_layout)
+        yr, _ = stack(x_raster, raster_layout)
     assert_close(raster_to_block_wo_padding(yr, vsa_layout=layout), y, "raster vs block order, 8 layers")
-    del yr, gate_r, grad
+    del yr, grad
     # Values and gradients of the last layer's call on the activations that reach it.
-    act = last_input.detach()
-    dy = _inputs(tokens, heads, 1, seed=1)[0]
-    _check_call(layout, act, act.clone(), act.clone(), _inputs(tokens, heads, 1, seed=4)[0], dy, [0, 23],
-                "block_order_stack_h24 layer 8")
+    dy = raster_to_block_wo_padding(_inputs(tokens, heads, 1, seed=1)[0], vsa_layout=layout)
+    q, k, v, gate = (t.detach() for t in last)
+    _check_call(layout, q, k, v, gate, dy, [0, 23], "block_order_stack_h24 layer 8")
