@@ -1,4 +1,7 @@
-// HBM-bound block kernels: one CTA per 64-slot block, one thread per 16-byte column chunk.
+// HBM-bound block kernels.  A CTA owns up to 128 16-byte column chunks of one 64-slot block and
+// splits the block's slots over two or more groups of threads, so that every thread keeps
+// several independent 16-byte loads in flight and a block of few heads still fills its SM;
+// wide rows (many heads) are split over several CTAs per block.
 //
 //   slots_pool   reads Q, K, V rows once through the slot map, writes the zero-padded slot
 //                tensors and the FP32 block means (sum of the slots / max(size, 1)) plus their
@@ -15,7 +18,9 @@ namespace vsa {
 
 namespace {
 
-constexpr int kChunk = 8;  // BF16 elements per 16-byte chunk
+constexpr int kChunk = 8;          // BF16 elements per 16-byte chunk
+constexpr int kCtaChunks = 128;    // column chunks per CTA at most (a multiple of 16 = one head)
+constexpr int kCtaThreads = 256;   // threads per CTA at most
 
 VSA_DEVICE void accumulate(float (&acc)[8], const uint4& v) {
   const uint32_t w[4] = {v.x, v.y, v.z, v.w};
@@ -27,8 +32,24 @@ VSA_DEVICE void accumulate(float (&acc)[8], const uint4& v) {
   }
 }
 
-__global__ void slots_pool_kernel(const PoolParams p) {
+// Launch shape shared by the block kernels: grid (blocks, column parts), `cols` chunks per CTA
+// and `groups` slot groups (threads = cols * groups; thread = (group, column chunk)).
+struct BlockShape {
+  int cols, groups, parts;
+};
+BlockShape block_shape(int chunks) {
+  BlockShape s;
+  s.parts = (chunks + kCtaChunks - 1) / kCtaChunks;
+  s.cols = (chunks + s.parts - 1) / s.parts;
+  s.cols = ((s.cols + 15) / 16) * 16;        // whole heads, so the 16-lane head sums stay together
+  s.groups = 1;  // a power of two (it divides the 64 slots), at most 8
+  while (s.groups < 8 && s.cols * s.groups * 2 <= kCtaThreads) s.groups *= 2;
+  return s;
+}
+
+__global__ void __launch_bounds__(kCtaThreads) slots_pool_kernel(const PoolParams p, int cols, int groups) {
   __shared__ long long rows[kBlock];
+  extern __shared__ float partial[];  // [groups - 1][cols][24] sums of the other slot groups
   const long long block = blockIdx.x;
   for (int i = threadIdx.x; i < kBlock; i += blockDim.x) {
     const long long slot = block * kBlock + i;
@@ -36,17 +57,19 @@ __global__ void slots_pool_kernel(const PoolParams p) {
   }
   __syncthreads();
   const int chunks = p.width / kChunk;
+  const int local = threadIdx.x % cols, group = threadIdx.x / cols;
+  const int c = blockIdx.y * cols + local;
+  const bool active = c < chunks;
   const int size = p.sizes[block];
-  const float inv = 1.f / static_cast<float>(size > 1 ? size : 1);
-  const long long coarse_row = (p.block_coarse != nullptr && p.mean_bf16 != nullptr) ? p.block_coarse[block] : -1;
+  const int per = kBlock / groups;  // slots of this thread: [group * per, group * per + per)
   const uint4* src[3] = {reinterpret_cast<const uint4*>(p.q), reinterpret_cast<const uint4*>(p.k),
                          reinterpret_cast<const uint4*>(p.v)};
   uint4* dst[3] = {reinterpret_cast<uint4*>(p.q_slots), reinterpret_cast<uint4*>(p.k_slots),
                    reinterpret_cast<uint4*>(p.v_slots)};
-  for (int c = threadIdx.x; c < chunks; c += blockDim.x) {
-    float acc[3][8] = {};
+  float acc[3][8] = {};
+  if (active) {
 #pragma unroll 4
-    for (int s = 0; s < kBlock; ++s) {
+    for (int s = group * per; s < (group + 1) * per; ++s) {
       const long long row = rows[s];
       const long long out = (block * kBlock + s) * chunks + c;
 #pragma unroll
@@ -57,21 +80,43 @@ __global__ void slots_pool_kernel(const PoolParams p) {
         accumulate(acc[t], v);
       }
     }
+  }
+  if (p.mean_f32 == nullptr && p.mean_bf16 == nullptr) return;
+  if (groups > 1) {
+    if (group > 0) {
+      float* mine = partial + (static_cast<size_t>(group - 1) * cols + local) * 24;
 #pragma unroll
-    for (int t = 0; t < 3; ++t) {
-      float mean[8];
+      for (int t = 0; t < 3; ++t)
 #pragma unroll
-      for (int e = 0; e < 8; ++e) mean[e] = acc[t][e] * inv;
-      if (p.mean_f32 != nullptr) {
-        float4* m = reinterpret_cast<float4*>(p.mean_f32 + (t * p.blocks + block) * p.width + c * kChunk);
-        m[0] = make_float4(mean[0], mean[1], mean[2], mean[3]);
-        m[1] = make_float4(mean[4], mean[5], mean[6], mean[7]);
-      }
-      if (coarse_row >= 0) {
-        uint4* m = reinterpret_cast<uint4*>(p.mean_bf16 + (t * p.coarse_rows + coarse_row) * p.width + c * kChunk);
-        *m = make_uint4(pack_bf16(mean[0], mean[1]), pack_bf16(mean[2], mean[3]), pack_bf16(mean[4], mean[5]),
-                        pack_bf16(mean[6], mean[7]));
-      }
+        for (int e = 0; e < 8; ++e) mine[t * 8 + e] = acc[t][e];
+    }
+    __syncthreads();
+    if (group > 0) return;
+    for (int g = 1; g < groups; ++g) {
+      const float* other = partial + (static_cast<size_t>(g - 1) * cols + local) * 24;
+#pragma unroll
+      for (int t = 0; t < 3; ++t)
+#pragma unroll
+        for (int e = 0; e < 8; ++e) acc[t][e] += other[t * 8 + e];
+    }
+  }
+  if (!active) return;
+  const float inv = 1.f / static_cast<float>(size > 1 ? size : 1);
+  const long long coarse_row = (p.block_coarse != nullptr && p.mean_bf16 != nullptr) ? p.block_coarse[block] : -1;
+#pragma unroll
+  for (int t = 0; t < 3; ++t) {
+    float mean[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) mean[e] = acc[t][e] * inv;
+    if (p.mean_f32 != nullptr) {
+      float4* m = reinterpret_cast<float4*>(p.mean_f32 + (t * p.blocks + block) * p.width + c * kChunk);
+      m[0] = make_float4(mean[0], mean[1], mean[2], mean[3]);
+      m[1] = make_float4(mean[4], mean[5], mean[6], mean[7]);
+    }
+    if (coarse_row >= 0) {
+      uint4* m = reinterpret_cast<uint4*>(p.mean_bf16 + (t * p.coarse_rows + coarse_row) * p.width + c * kChunk);
+      *m = make_uint4(pack_bf16(mean[0], mean[1]), pack_bf16(mean[2], mean[3]), pack_bf16(mean[4], mean[5]),
+                      pack_bf16(mean[6], mean[7]));
     }
   }
 }
@@ -83,8 +128,9 @@ VSA_DEVICE float head_sum(float x) {
   return x;
 }
 
-__global__ void merge_bwd_kernel(const MergeBwdParams p) {
+__global__ void __launch_bounds__(kCtaThreads) merge_bwd_kernel(const MergeBwdParams p, int cols, int groups) {
   __shared__ long long rows[kBlock];
+  extern __shared__ float partial[];  // [groups - 1][cols][8] dcoarse sums of the other slot groups
   const long long block = blockIdx.x;
   for (int i = threadIdx.x; i < kBlock; i += blockDim.x) {
     const long long slot = block * kBlock + i;
@@ -94,71 +140,82 @@ __global__ void merge_bwd_kernel(const MergeBwdParams p) {
   const int width = p.heads * kDim;
   const int chunks = width / kChunk;
   const long long slots = p.blocks * kBlock;
+  const int local = threadIdx.x % cols, group = threadIdx.x / cols;
+  const int c = blockIdx.y * cols + local;
+  // `cols` is a multiple of 16, so an aligned group of 16 lanes holds one head of one slot group.
+  const bool active = c < chunks;
+  const int head = active ? (c * kChunk) / kDim : 0;
+  const int per = kBlock / groups;
   const long long coarse_row = (p.block_coarse != nullptr && p.coarse != nullptr) ? p.block_coarse[block] : -1;
   const uint4* grad = reinterpret_cast<const uint4*>(p.grad);
   const uint4* gate = reinterpret_cast<const uint4*>(p.gate);
   const uint4* fine = reinterpret_cast<const uint4*>(p.o_slots);
-  // blockDim is a multiple of 32 and chunks a multiple of 16, so whole 16-lane groups stay together.
-  for (int c0 = 0; c0 < chunks; c0 += blockDim.x) {
-    const int c = c0 + threadIdx.x;
-    const bool active = c < chunks;
-    const int head = active ? (c * kChunk) / kDim : 0;
-    float cz[8] = {};
-    if (active && coarse_row >= 0) {
-      const uint4 v = __ldg(reinterpret_cast<const uint4*>(p.coarse) + coarse_row * chunks + c);
-      float z[8] = {};
-      accumulate(z, v);
+  float cz[8] = {};
+  if (active && coarse_row >= 0) accumulate(cz, __ldg(reinterpret_cast<const uint4*>(p.coarse) + coarse_row * chunks + c));
+  float dc[8] = {};
+#pragma unroll 2
+  for (int s = group * per; s < (group + 1) * per; ++s) {
+    const long long row = rows[s];
+    const long long slot = block * kBlock + s;
+    float g[8] = {}, o[8] = {};
+    uint4 gv = make_uint4(0, 0, 0, 0);
+    if (active && row >= 0) {
+      gv = __ldg(grad + row * chunks + c);
+      const uint4 ov = __ldg(fine + slot * chunks + c);
+      uint4 tv = make_uint4(0, 0, 0, 0);
+      if (coarse_row >= 0) tv = __ldg(gate + row * chunks + c);
+      accumulate(g, gv);
+      accumulate(o, ov);
+      if (coarse_row >= 0) {
+        float gt[8] = {};
+        accumulate(gt, tv);
+        float dg[8];
 #pragma unroll
-      for (int e = 0; e < 8; ++e) cz[e] = z[e];
-    }
-    float dc[8] = {};
-    for (int s = 0; s < kBlock; ++s) {
-      const long long row = rows[s];
-      const long long slot = block * kBlock + s;
-      float g[8] = {}, o[8] = {};
-      uint4 gv = make_uint4(0, 0, 0, 0);
-      if (active && row >= 0) {
-        gv = __ldg(grad + row * chunks + c);
-        accumulate(g, gv);
-        accumulate(o, __ldg(fine + slot * chunks + c));
-        if (coarse_row >= 0) {
-          float gt[8] = {};
-          accumulate(gt, __ldg(gate + row * chunks + c));
-          float dg[8];
-#pragma unroll
-          for (int e = 0; e < 8; ++e) {
-            dg[e] = g[e] * cz[e];
-            dc[e] += g[e] * gt[e];
-          }
-          if (p.dgate != nullptr)
-            reinterpret_cast<uint4*>(p.dgate)[row * chunks + c] =
-                make_uint4(pack_bf16(dg[0], dg[1]), pack_bf16(dg[2], dg[3]), pack_bf16(dg[4], dg[5]),
-                           pack_bf16(dg[6], dg[7]));
-        } else if (p.dgate != nullptr) {
-          reinterpret_cast<uint4*>(p.dgate)[row * chunks + c] = make_uint4(0, 0, 0, 0);
+        for (int e = 0; e < 8; ++e) {
+          dg[e] = g[e] * cz[e];
+          dc[e] += g[e] * gt[e];
         }
+        if (p.dgate != nullptr)
+          reinterpret_cast<uint4*>(p.dgate)[row * chunks + c] =
+              make_uint4(pack_bf16(dg[0], dg[1]), pack_bf16(dg[2], dg[3]), pack_bf16(dg[4], dg[5]),
+                         pack_bf16(dg[6], dg[7]));
+      } else if (p.dgate != nullptr) {
+        reinterpret_cast<uint4*>(p.dgate)[row * chunks + c] = make_uint4(0, 0, 0, 0);
       }
-      if (active && p.grad_slots != nullptr) reinterpret_cast<uint4*>(p.grad_slots)[slot * chunks + c] = gv;
-      float part = 0.f;
-#pragma unroll
-      for (int e = 0; e < 8; ++e) part += g[e] * o[e];
-      part = head_sum(part);
-      if (active && (threadIdx.x & 15) == 0) p.delta[head * slots + slot] = part;
     }
-    if (coarse_row >= 0 && p.dcoarse != nullptr) {
-      const uint4 packed = make_uint4(pack_bf16(dc[0], dc[1]), pack_bf16(dc[2], dc[3]), pack_bf16(dc[4], dc[5]),
-                                      pack_bf16(dc[6], dc[7]));
-      if (active) reinterpret_cast<uint4*>(p.dcoarse)[coarse_row * chunks + c] = packed;
-      float rounded[8] = {};
-      accumulate(rounded, packed);
-      float part = 0.f;
+    if (active && p.grad_slots != nullptr) reinterpret_cast<uint4*>(p.grad_slots)[slot * chunks + c] = gv;
+    float part = 0.f;
 #pragma unroll
-      for (int e = 0; e < 8; ++e) part += rounded[e] * cz[e];
-      part = head_sum(part);
-      if (active && p.coarse_delta != nullptr && (threadIdx.x & 15) == 0)
-        p.coarse_delta[head * p.coarse_rows + coarse_row] = part;
+    for (int e = 0; e < 8; ++e) part += g[e] * o[e];
+    part = head_sum(part);
+    if (active && (threadIdx.x & 15) == 0) p.delta[head * slots + slot] = part;
+  }
+  if (coarse_row < 0 || p.dcoarse == nullptr) return;  // uniform over the CTA
+  if (groups > 1) {
+    if (group > 0) {
+      float* mine = partial + (static_cast<size_t>(group - 1) * cols + local) * 8;
+#pragma unroll
+      for (int e = 0; e < 8; ++e) mine[e] = dc[e];
+    }
+    __syncthreads();
+    if (group > 0) return;
+    for (int g2 = 1; g2 < groups; ++g2) {
+      const float* other = partial + (static_cast<size_t>(g2 - 1) * cols + local) * 8;
+#pragma unroll
+      for (int e = 0; e < 8; ++e) dc[e] += other[e];
     }
   }
+  const uint4 packed = make_uint4(pack_bf16(dc[0], dc[1]), pack_bf16(dc[2], dc[3]), pack_bf16(dc[4], dc[5]),
+                                  pack_bf16(dc[6], dc[7]));
+  if (active) reinterpret_cast<uint4*>(p.dcoarse)[coarse_row * chunks + c] = packed;
+  float rounded[8] = {};
+  accumulate(rounded, packed);
+  float part = 0.f;
+#pragma unroll
+  for (int e = 0; e < 8; ++e) part += rounded[e] * cz[e];
+  part = head_sum(part);
+  if (active && p.coarse_delta != nullptr && (threadIdx.x & 15) == 0)
+    p.coarse_delta[head * p.coarse_rows + coarse_row] = part;
 }
 
 // Ring epilogue of the forward pass: FP32 fine output in slot order -> BF16 copy for the backward
@@ -243,14 +300,19 @@ int block_threads(int chunks) {
 
 cudaError_t launch_slots_pool(const PoolParams& params, cudaStream_t stream) {
   if (params.blocks == 0) return cudaSuccess;
-  slots_pool_kernel<<<static_cast<unsigned>(params.blocks), block_threads(params.width / kChunk), 0, stream>>>(params);
+  const BlockShape shape = block_shape(params.width / kChunk);
+  const size_t smem = static_cast<size_t>(shape.groups - 1) * shape.cols * 24 * sizeof(float);
+  dim3 grid(static_cast<unsigned>(params.blocks), shape.parts);
+  slots_pool_kernel<<<grid, shape.cols * shape.groups, smem, stream>>>(params, shape.cols, shape.groups);
   return cudaGetLastError();
 }
 
 cudaError_t launch_merge_bwd(const MergeBwdParams& params, cudaStream_t stream) {
   if (params.blocks == 0) return cudaSuccess;
-  merge_bwd_kernel<<<static_cast<unsigned>(params.blocks), block_threads(params.heads * kDim / kChunk), 0, stream>>>(
-      params);
+  const BlockShape shape = block_shape(params.heads * kDim / kChunk);
+  const size_t smem = static_cast<size_t>(shape.groups - 1) * shape.cols * 8 * sizeof(float);
+  dim3 grid(static_cast<unsigned>(params.blocks), shape.parts);
+  merge_bwd_kernel<<<grid, shape.cols * shape.groups, smem, stream>>>(params, shape.cols, shape.groups);
   return cudaGetLastError();
 }
 
