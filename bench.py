@@ -506,7 +506,8 @@ def main():
         result["parity"] = parity
     peaks = measured_peaks()
     if not args.no_phases:
-        phases = measure_phases(forward, leaves, dy, max(args.steps, 5), world, use_graph=world == 1)
+        phases = measure_phases(forward, leaves, dy, min(max(args.steps, 5), 10 if world > 1 else 50), world,
+                                use_graph=world == 1)
         phases["tflops_total"] = total.item() / (phases["total_ms"] * 1e-3) / 1e12
         result["phases"] = phases
     with _cabi.trace() as tr:

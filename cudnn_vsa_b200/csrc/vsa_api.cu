@@ -276,6 +276,8 @@ int vsa_fine_bwd(const void* q, const void* k, const void* v, const void* d_o, i
   p.dk_f32 = dk_f32;
   p.dv_f32 = dv_f32;
   p.f32_accumulate = f32_accumulate;
+  p.first_kv_blocks = (parts >> 8) & 0xFFFFF;
+  if (p.first_kv_blocks > kv_blocks) p.first_kv_blocks = static_cast<int>(kv_blocks);
   p.q_out_rows = q_out_rows;
   p.kv_out_rows = kv_out_rows;
   p.q_slots = q_blocks * vsa::kBlock;

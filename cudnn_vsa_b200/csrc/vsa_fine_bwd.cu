@@ -164,7 +164,19 @@ __global__ void __launch_bounds__(kDkvThreads, 1) fine_bwd_dkv_kernel(const __gr
   extern __shared__ uint8_t smem_raw[];
   DkvSmem& sm = *reinterpret_cast<DkvSmem*>(smem_raw + ((1024 - (smem_u32(smem_raw) & 1023)) & 1023));
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int kvb = blockIdx.x, head = blockIdx.y;
+  // CTA order: the `first_kv_blocks` leading KV blocks of every head, then the rest head by head.
+  int kvb, head;
+  {
+    const long long id = blockIdx.x, first = p.first_kv_blocks, early = first * p.heads;
+    if (id < early) {
+      head = static_cast<int>(id / first);
+      kvb = static_cast<int>(id - head * first);
+    } else {
+      const long long rest = p.kv_blocks - first, at = id - early;
+      head = static_cast<int>(at / rest);
+      kvb = static_cast<int>(first + (at - head * rest));
+    }
+  }
   const int group = (warp >> 2) & 1;  // score-math warpgroup (warps 0..7 only)
   const int qrow = tid & 127;         // query row of the pair owned by this thread (math role) / head dim (epilogue)
   const uint32_t* mask = p.kv_mask + (static_cast<long long>(head) * p.kv_blocks + kvb) * p.mask_words;
@@ -420,8 +432,9 @@ cudaError_t launch_fine_bwd_dkv(const FineBwdParams& params, cudaStream_t stream
   cudaError_t err = cudaFuncSetAttribute(fine_bwd_dkv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          static_cast<int>(smem));
   if (err != cudaSuccess) return err;
-  dim3 grid(params.kv_blocks, params.heads);
-  fine_bwd_dkv_kernel<<<grid, kDkvThreads, smem, stream>>>(params);
+  const long long ctas = static_cast<long long>(params.kv_blocks) * params.heads;
+  if (ctas > 0x7fffffffLL) return cudaErrorInvalidValue;
+  fine_bwd_dkv_kernel<<<static_cast<unsigned>(ctas), kDkvThreads, smem, stream>>>(params);
   return cudaGetLastError();
 }
 

@@ -72,6 +72,10 @@ struct FineBwdParams {
   float* dk_f32;
   float* dv_f32;
   int f32_accumulate;
+  // dK/dV kernel: the first `first_kv_blocks` KV blocks are scheduled ahead of all others, for
+  // every head (blocks that every query block lists run ten times longer than the rest; started
+  // last they would be the tail of the launch).
+  int first_kv_blocks;
   long long q_out_rows, kv_out_rows;
   long long q_slots, kv_slots;
   int q_blocks, kv_blocks, heads;

@@ -57,6 +57,7 @@ class _DevicePlan:
     spans: tuple                # (q_begin, q_end, kv_first, kv_last, keep, cursor) per region needing top-k
     status: torch.Tensor        # int32 [1] device error word shared by the kernels of this layout
     sizes: torch.Tensor | None  # block sizes, or None when every block is full
+    early_kv: tuple = ()        # ring: per owner, leading always-visible KV blocks to schedule first
 
 
 def _coarse_plan(pairs, q_blocks, kv_blocks, device):
@@ -98,6 +99,27 @@ def _coarse_plan(pairs, q_blocks, kv_blocks, device):
                        q_sizes=dev(np.asarray(q_sizes or [0], dtype=np.int32)))
 
 
+def _early_kv_blocks(layout):
+    """Ring layouts: for each owner, how many of its leading block slots hold always-visible
+    (dense) blocks of the first sample.  Every local query block of that sample lists them at
+    every ring step, so their dK/dV CTAs run far longer than the others and are started first
+    (``vsa_fine_bwd``'s scheduling hint).  0 where the dense blocks are not at the front."""
+    ring = layout.ring
+    if ring is None or not ring.local_groups:
+        return ()
+    group = ring.local_groups[0][0]
+    if group.dense_only or not group.dense_blocks_num:
+        return (0,) * ring.size
+    capacity = ring.peer_block_sizes.shape[1]
+    where = ring.global_to_gather[group.start:group.start + group.dense_blocks_num].cpu().numpy()
+    owners, local = where // capacity, where % capacity
+    out = []
+    for owner in range(ring.size):
+        ids = np.sort(local[owners == owner])
+        out.append(int(len(ids)) if len(ids) and np.array_equal(ids, np.arange(len(ids))) else 0)
+    return tuple(out)
+
+
 def device_plan(layout):
     """Derived device metadata of a layout, built once and cached on the layout object."""
     plan = getattr(layout, "_b200_plan", None)
@@ -121,7 +143,8 @@ def device_plan(layout):
             coarse = _coarse_plan(pairs, layout.blocks, layout.ring.global_to_gather.numel(), device)
     plan = _DevicePlan(coarse=coarse, spans=tuple(spans),
                        status=torch.zeros(1, dtype=torch.int32, device=device),
-                       sizes=None if layout.all_blocks_full else layout.block_sizes)
+                       sizes=None if layout.all_blocks_full else layout.block_sizes,
+                       early_kv=_early_kv_blocks(layout))
     layout._b200_plan = plan
     return plan
 

@@ -146,8 +146,9 @@ def _gather_rows(x, row_map):
 
 
 def _bwd_call(q, k, v, d_o, index, counts, sizes_q, sizes_kv, scale, lse, delta, mask, status, *, parts,
-              dq=None, dk=None, dv=None, dq_f32=None, dk_f32=None, dv_f32=None, accumulate=0):
+              dq=None, dk=None, dv=None, dq_f32=None, dk_f32=None, dv_f32=None, accumulate=0, early_kv=0):
     heads = q.shape[1]
+    parts |= int(early_kv) << 8  # scheduling hint of the dK/dV kernel
     q_blocks, kv_blocks = q.shape[0] // BLOCK, k.shape[0] // BLOCK
     with _cabi.mark("ring_step_dq" if parts & 2 else "ring_step_dkv"):
         _bwd_launch(q, k, v, d_o, index, counts, sizes_q, sizes_kv, scale, lse, delta, mask, status, parts, dq, dk,
@@ -160,7 +161,7 @@ def _bwd_launch(q, k, v, d_o, index, counts, sizes_q, sizes_kv, scale, lse, delt
                index.stride(0), counts.stride(0), index.shape[-1], _p(sizes_q), _p(sizes_kv), scale, _p(lse),
                _p(delta), _p(mask), _p(dq), _p(dk), _p(dv), q.shape[0], k.shape[0], None, None, None, None, None,
                0, None, None, _p(dq_f32), _p(dk_f32), _p(dv_f32), accumulate, parts, _p(status), _cabi.stream(),
-               launches=bin(parts).count("1"))
+               launches=bin(parts & 7).count("1"))
 
 
 class _RingVSAFunction(torch.autograd.Function):
@@ -289,7 +290,8 @@ class _RingVSAFunction(torch.autograd.Function):
             _bwd_call(*common, parts=3, dq_f32=dq_acc, accumulate=1)
             if pairs:
                 join_exchange(rt)
-            _bwd_call(*common, parts=4, dk_f32=target[0], dv_f32=target[1], accumulate=1 if step else 0)
+            _bwd_call(*common, parts=4, dk_f32=target[0], dv_f32=target[1], accumulate=1 if step else 0,
+                      early_kv=plan.early_kv[owner])
             accumulated = target
         dq, dk, dv = (torch.empty_like(grad) for _ in range(3))
         sizes = layout.block_sizes

@@ -150,7 +150,11 @@ int64_t vsa_kv_mask_words(int64_t q_blocks);
  *   instead (added to their content when f32_accumulate != 0) - the ring path's running dQ and
  *   travelling dK / dV (vsa_kernels.py:356-372).
  *   `parts` selects what runs: bit 0 rebuilds kv_mask, bit 1 the dQ kernel, bit 2 the dK/dV
- *   kernel (7 = everything; the pieces can be launched and timed one by one).
+ *   kernel (7 = everything; the pieces can be launched and timed one by one).  Bits 8-27 hold a
+ *   scheduling hint for the dK/dV kernel: that many leading KV blocks (ids 0 .. hint-1) start
+ *   before all others for every head.  Pass the number of always-visible blocks at the front of
+ *   the KV numbering: every query block lists them, so they run many times longer than the rest
+ *   and would otherwise finish last.  The hint changes launch order only, never results.
  * Replaces vsa_core.py:23-30, 42-47 (cuDNN BSA backward), the FA4 backward of the coarse call,
  * the pooling adjoint of vsa_kernels.py:161-176 and the slot->row gathers of :86-96. */
 int vsa_fine_bwd(const void* q, const void* k, const void* v, const void* d_o, int64_t q_blocks, int64_t kv_blocks,
