@@ -101,7 +101,8 @@ def _coarse_plan(pairs, q_blocks, kv_blocks, device):
 
 def _early_kv_blocks(layout):
     """Ring layouts: for each owner, how many of its leading block slots hold always-visible
-    (dense) blocks of the first sample.  Every local query block of that sample lists them at
+    (dense) blocks of the first sample.  (On a single device the hint was measured at 2, 4 and 24
+    heads and changes nothing: there the long CTAs of one head finish under the next head's work.)  Every local query block of that sample lists them at
     every ring step, so their dK/dV CTAs run far longer than the others and are started first
     (``vsa_fine_bwd``'s scheduling hint).  0 where the dense blocks are not at the front."""
     ring = layout.ring
