@@ -68,7 +68,7 @@ __global__ void __launch_bounds__(kCtaThreads) slots_pool_kernel(const PoolParam
                    reinterpret_cast<uint4*>(p.v_slots)};
   float acc[3][8] = {};
   if (active) {
-#pragma unroll 4
+#pragma unroll 8
     for (int s = group * per; s < (group + 1) * per; ++s) {
       const long long row = rows[s];
       const long long out = (block * kBlock + s) * chunks + c;
@@ -223,14 +223,17 @@ __global__ void __launch_bounds__(kCtaThreads) merge_bwd_kernel(const MergeBwdPa
 __global__ void gate_merge_kernel(const float* __restrict__ fine, const int64_t* __restrict__ slot_row,
                                   const int32_t* __restrict__ block_coarse, const __nv_bfloat16* __restrict__ gate,
                                   const __nv_bfloat16* __restrict__ coarse, __nv_bfloat16* __restrict__ o_slots,
-                                  __nv_bfloat16* __restrict__ out, int width, long long out_rows) {
+                                  __nv_bfloat16* __restrict__ out, int width, long long out_rows, int cols,
+                                  int groups) {
   const long long block = blockIdx.x;
   const int chunks = width / kChunk;
   const long long coarse_row = (block_coarse != nullptr && coarse != nullptr) ? block_coarse[block] : -1;
-  for (int c = threadIdx.x; c < chunks; c += blockDim.x) {
+  const int c = blockIdx.y * cols + threadIdx.x % cols, group = threadIdx.x / cols, per = kBlock / groups;
+  if (c < chunks) {
     float cz[8] = {};
     if (coarse_row >= 0) accumulate(cz, __ldg(reinterpret_cast<const uint4*>(coarse) + coarse_row * chunks + c));
-    for (int s = 0; s < kBlock; ++s) {
+#pragma unroll 4
+    for (int s = group * per; s < (group + 1) * per; ++s) {
       const long long slot = block * kBlock + s;
       const float4* src = reinterpret_cast<const float4*>(fine + slot * width + c * kChunk);
       const float4 a = src[0], b = src[1];
@@ -256,14 +259,15 @@ __global__ void gate_merge_kernel(const float* __restrict__ fine, const int64_t*
 __global__ void grad_finish_kernel(const float* __restrict__ acc, const int64_t* __restrict__ slot_row,
                                    const void* __restrict__ pool, int pool_f32, const int32_t* __restrict__ block_map,
                                    const int32_t* __restrict__ sizes, __nv_bfloat16* __restrict__ out, int width,
-                                   long long out_rows) {
+                                   long long out_rows, int cols, int groups) {
   const long long block = blockIdx.x;
   const int chunks = width / kChunk;
   long long prow = -1;
   if (pool != nullptr) prow = pool_f32 ? block : (block_map != nullptr ? block_map[block] : -1);
   const int size = sizes != nullptr ? sizes[block] : kBlock;
   const float inv = 1.f / static_cast<float>(size > 1 ? size : 1);
-  for (int c = threadIdx.x; c < chunks; c += blockDim.x) {
+  const int c = blockIdx.y * cols + threadIdx.x % cols, group = threadIdx.x / cols, per = kBlock / groups;
+  if (c < chunks) {
     float term[8] = {};
     if (prow >= 0) {
       if (pool_f32) {
@@ -277,7 +281,8 @@ __global__ void grad_finish_kernel(const float* __restrict__ acc, const int64_t*
 #pragma unroll
       for (int e = 0; e < 8; ++e) term[e] *= inv;
     }
-    for (int s = 0; s < kBlock; ++s) {
+#pragma unroll 4
+    for (int s = group * per; s < (group + 1) * per; ++s) {
       const long long slot = block * kBlock + s;
       const long long row = slot_row != nullptr ? slot_row[slot] : slot;
       if (row < 0 || row >= out_rows) continue;
@@ -289,11 +294,6 @@ __global__ void grad_finish_kernel(const float* __restrict__ acc, const int64_t*
           make_uint4(pack_bf16(f[0], f[1]), pack_bf16(f[2], f[3]), pack_bf16(f[4], f[5]), pack_bf16(f[6], f[7]));
     }
   }
-}
-
-int block_threads(int chunks) {
-  int threads = ((chunks + 31) / 32) * 32;
-  return threads > 512 ? 512 : threads;
 }
 
 }  // namespace
@@ -322,8 +322,9 @@ cudaError_t launch_gate_merge(const float* fine, const int64_t* slot_row, const 
                               cudaStream_t stream) {
   if (blocks == 0) return cudaSuccess;
   const int width = heads * kDim;
-  gate_merge_kernel<<<static_cast<unsigned>(blocks), block_threads(width / kChunk), 0, stream>>>(
-      fine, slot_row, block_coarse, gate, coarse, o_slots, out, width, out_rows);
+  const BlockShape shape = block_shape(width / kChunk);
+  gate_merge_kernel<<<dim3(static_cast<unsigned>(blocks), shape.parts), shape.cols * shape.groups, 0, stream>>>(
+      fine, slot_row, block_coarse, gate, coarse, o_slots, out, width, out_rows, shape.cols, shape.groups);
   return cudaGetLastError();
 }
 
@@ -332,8 +333,9 @@ cudaError_t launch_grad_finish(const float* acc, const int64_t* slot_row, const 
                                int heads, long long out_rows, cudaStream_t stream) {
   if (blocks == 0) return cudaSuccess;
   const int width = heads * kDim;
-  grad_finish_kernel<<<static_cast<unsigned>(blocks), block_threads(width / kChunk), 0, stream>>>(
-      acc, slot_row, pool, pool_f32, block_map, sizes, out, width, out_rows);
+  const BlockShape shape = block_shape(width / kChunk);
+  grad_finish_kernel<<<dim3(static_cast<unsigned>(blocks), shape.parts), shape.cols * shape.groups, 0, stream>>>(
+      acc, slot_row, pool, pool_f32, block_map, sizes, out, width, out_rows, shape.cols, shape.groups);
   return cudaGetLastError();
 }
 
