@@ -187,3 +187,20 @@ def test_ring_over_nccl_matches_single_device():
     if log_dir:  # keep the workers' PARITY lines as evidence of the run
         Path(log_dir, f"ring_worker_r{world}.log").write_text(done.stdout + done.stderr[-3000:])
     assert done.returncode == 0, done.stdout[-3000:] + done.stderr[-3000:]
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_ulysses_over_nccl_matches_single_device():
+    """Ulysses on two ranks, and Ring x Ulysses (U=2, R=2) when four GPUs are visible."""
+    shapes = [(2, 1)] + ([(2, 2)] if torch.cuda.device_count() >= 4 else [])
+    for ulysses_size, ring_size in shapes:
+        world = ulysses_size * ring_size
+        cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
+               "--master-addr", "127.0.0.1", "--master-port", "29633", str(ROOT / "tests" / "ulysses_worker.py"),
+               "--ulysses", str(ulysses_size), "--ring", str(ring_size)]
+        env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+        done = subprocess.run(cmd, capture_output=True, text=True, timeout=900, env=env)
+        log_dir = os.environ.get("VSA_TEST_LOG_DIR")
+        if log_dir:
+            Path(log_dir, f"ulysses_worker_u{ulysses_size}r{ring_size}.log").write_text(done.stdout + done.stderr[-3000:])
+        assert done.returncode == 0, done.stdout[-3000:] + done.stderr[-3000:]
