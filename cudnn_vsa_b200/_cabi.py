@@ -21,6 +21,7 @@ SIGNATURES = {
     "vsa_row_gather": (_I32, [_P, _P, _P, _I64, _I64, _P]),
     "vsa_row_scatter": (_I32, [_P, _P, _P, _I64, _I64, _P]),
     "vsa_slots_pool": (_I32, [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I64, _I64, _I32, _P]),
+    "vsa_slots_pool_strided": (_I32, [_P, _P, _P, _I64, _I64, _P, _P, _P, _P, _P, _P, _P, _P, _I64, _I64, _I32, _P]),
     "vsa_route_scratch_bytes": (_I64, [_I64, _I64, _I32]),
     "vsa_route": (_I32, [_P, _P, _I32, _I32, _I32, _I32, _I32, _I32, _I32, _I32, _I32, _P, _I64, _I32, _P,
                          _I64, _P]),
@@ -28,12 +29,18 @@ SIGNATURES = {
     "vsa_route_static": (_I32, [_P, _P, _I32, _I32, _I32, _I32, _I32, _I32, _I32, _I32, _I32, _P, _I64, _I32, _P]),
     "vsa_fine_fwd": (_I32, [_P, _P, _P, _I64, _I64, _I32, _P, _P, _I64, _I64, _I32, _P, _F, _P, _P, _P, _P,
                             _P, _P, _P, _I64, _P, _P]),
+    "vsa_fine_fwd_strided": (_I32, [_P, _P, _P, _I64, _I64, _I32, _P, _P, _I64, _I64, _I32, _P, _F, _P, _P, _P, _P,
+                                    _P, _I64, _I64, _P, _P, _I64, _P, _P]),
     "vsa_fine_fwd_running": (_I32, [_P, _P, _P, _I64, _I64, _I32, _P, _P, _I64, _I64, _I32, _P, _F, _P, _P, _P, _P]),
     "vsa_merge_bwd": (_I32, [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I64, _I64, _I32, _P]),
+    "vsa_merge_bwd_strided": (_I32, [_P, _P, _I64, _I64, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I64, _I64, _I32, _P]),
     "vsa_kv_mask_words": (_I64, [_I64]),
     "vsa_fine_bwd": (_I32, [_P, _P, _P, _P, _I64, _I64, _I32, _P, _P, _I64, _I64, _I32, _P, _P, _F, _P, _P,
                             _P, _P, _P, _P, _I64, _I64, _P, _P, _P, _P, _P, _I32, _P, _P, _P, _P, _P, _I32,
                             _I32, _P, _P]),
+    "vsa_fine_bwd_strided": (_I32, [_P, _P, _P, _P, _I64, _I64, _I32, _P, _P, _I64, _I64, _I32, _P, _P, _F, _P, _P,
+                                    _P, _P, _P, _P, _I64, _I64, _I64, _I64, _P, _P, _P, _P, _P, _I32, _P, _P, _I32,
+                                    _P, _P]),
     "vsa_partition_indices": (_I32, [_P, _P, _P, _P, _P, _I64, _I32, _I32, _I32, _I32, _I64, _I64, _P]),
     "vsa_merge_partial": (_I32, [_P, _P, _P, _P, _I64, _I32, _P]),
     "vsa_gate_merge": (_I32, [_P, _P, _P, _P, _P, _P, _P, _I64, _I32, _I64, _P]),

@@ -69,15 +69,27 @@ int vsa_row_scatter(const void* x, const int64_t* rows, void* out, int64_t in_ro
   return from_cuda(vsa::launch_row_scatter(x, rows, out, in_rows, row_bytes, as_stream(stream)));
 }
 
-int vsa_slots_pool(const void* q, const void* k, const void* v, const int64_t* slot_row, const int32_t* block_sizes,
-                   void* q_slots, void* k_slots, void* v_slots, float* mean_f32, const int32_t* block_coarse,
-                   void* mean_bf16, int64_t coarse_rows, int64_t blocks, int32_t heads, void* stream) {
+}  // extern "C" (reopened below)
+
+namespace {
+
+int slots_pool_common(const void* q, const void* k, const void* v, int64_t in_row_stride, int64_t in_head_stride,
+                      const int64_t* slot_row, const int32_t* block_sizes, void* q_slots, void* k_slots,
+                      void* v_slots, float* mean_f32, const int32_t* block_coarse, void* mean_bf16,
+                      int64_t coarse_rows, int64_t blocks, int32_t heads, void* stream) {
   if (q == nullptr || k == nullptr || v == nullptr || block_sizes == nullptr || blocks < 0 || heads <= 0)
+    return vsa::kBadArgument;
+  // Rows are read in 16-byte units.
+  if (in_row_stride < static_cast<int64_t>(heads) * vsa::kDim || in_head_stride < vsa::kDim ||
+      (in_row_stride % 8) != 0 || (in_head_stride % 8) != 0 ||
+      ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(v)) & 15) != 0)
     return vsa::kBadArgument;
   vsa::PoolParams p{};
   p.q = static_cast<const __nv_bfloat16*>(q);
   p.k = static_cast<const __nv_bfloat16*>(k);
   p.v = static_cast<const __nv_bfloat16*>(v);
+  p.in_row_stride = in_row_stride;
+  p.in_head_stride = in_head_stride;
   p.slot_row = slot_row;
   p.sizes = block_sizes;
   p.q_slots = static_cast<__nv_bfloat16*>(q_slots);
@@ -90,6 +102,30 @@ int vsa_slots_pool(const void* q, const void* k, const void* v, const int64_t* s
   p.blocks = blocks;
   p.width = heads * vsa::kDim;
   return from_cuda(vsa::launch_slots_pool(p, as_stream(stream)));
+}
+
+bool bad_strides(int64_t row_stride, int64_t head_stride, int32_t heads) {
+  return row_stride < static_cast<int64_t>(heads) * vsa::kDim || head_stride < vsa::kDim || (row_stride % 8) != 0 ||
+         (head_stride % 8) != 0;
+}
+
+}  // namespace
+
+extern "C" {
+
+int vsa_slots_pool(const void* q, const void* k, const void* v, const int64_t* slot_row, const int32_t* block_sizes,
+                   void* q_slots, void* k_slots, void* v_slots, float* mean_f32, const int32_t* block_coarse,
+                   void* mean_bf16, int64_t coarse_rows, int64_t blocks, int32_t heads, void* stream) {
+  return slots_pool_common(q, k, v, static_cast<int64_t>(heads) * vsa::kDim, vsa::kDim, slot_row, block_sizes, q_slots,
+                           k_slots, v_slots, mean_f32, block_coarse, mean_bf16, coarse_rows, blocks, heads, stream);
+}
+
+int vsa_slots_pool_strided(const void* q, const void* k, const void* v, int64_t in_row_stride, int64_t in_head_stride,
+                           const int64_t* slot_row, const int32_t* block_sizes, void* q_slots, void* k_slots,
+                           void* v_slots, float* mean_f32, const int32_t* block_coarse, void* mean_bf16,
+                           int64_t coarse_rows, int64_t blocks, int32_t heads, void* stream) {
+  return slots_pool_common(q, k, v, in_row_stride, in_head_stride, slot_row, block_sizes, q_slots, k_slots, v_slots,
+                           mean_f32, block_coarse, mean_bf16, coarse_rows, blocks, heads, stream);
 }
 
 int64_t vsa_route_scratch_bytes(int64_t rows, int64_t region, int32_t heads) {
@@ -131,8 +167,11 @@ int fine_fwd_common(const void* q, const void* k, const void* v, int64_t q_block
                     const int32_t* indices, const int32_t* counts, int64_t index_head_stride,
                     int64_t count_head_stride, int32_t capacity, const int32_t* kv_sizes, float scale, void* o_slots,
                     float* lse, float* o_running, const int64_t* slot_row, const int32_t* block_coarse,
-                    const void* gate, const void* coarse, void* out, int64_t out_rows, int32_t* status,
-                    void* stream) {
+                    const void* gate, int64_t gate_row_stride, int64_t gate_head_stride, const void* coarse,
+                    void* out, int64_t out_rows, int32_t* status, void* stream) {
+  if (gate != nullptr && (bad_strides(gate_row_stride, gate_head_stride, heads) ||
+                          (reinterpret_cast<uintptr_t>(gate) & 15) != 0))
+    return vsa::kBadArgument;
   if (q == nullptr || k == nullptr || v == nullptr || indices == nullptr || counts == nullptr ||
       (o_slots == nullptr && o_running == nullptr) || lse == nullptr || q_blocks < 0 || kv_blocks <= 0 ||
       heads <= 0 || capacity <= 0)
@@ -160,6 +199,8 @@ int fine_fwd_common(const void* q, const void* k, const void* v, int64_t q_block
   p.slot_row = slot_row;
   p.block_coarse = block_coarse;
   p.gate = static_cast<const __nv_bfloat16*>(gate);
+  p.gate_row_stride = gate_row_stride;
+  p.gate_head_stride = gate_head_stride;
   p.coarse = static_cast<const __nv_bfloat16*>(coarse);
   p.out = static_cast<__nv_bfloat16*>(out);
   p.out_rows = out_rows;
@@ -182,8 +223,20 @@ int vsa_fine_fwd(const void* q, const void* k, const void* v, int64_t q_blocks, 
                  void* out, int64_t out_rows, int32_t* status, void* stream) {
   if (o_slots == nullptr) return vsa::kBadArgument;
   return fine_fwd_common(q, k, v, q_blocks, kv_blocks, heads, indices, counts, index_head_stride, count_head_stride,
-                         capacity, kv_sizes, scale, o_slots, lse, nullptr, slot_row, block_coarse, gate, coarse, out,
-                         out_rows, status, stream);
+                         capacity, kv_sizes, scale, o_slots, lse, nullptr, slot_row, block_coarse, gate,
+                         static_cast<int64_t>(heads) * vsa::kDim, vsa::kDim, coarse, out, out_rows, status, stream);
+}
+
+int vsa_fine_fwd_strided(const void* q, const void* k, const void* v, int64_t q_blocks, int64_t kv_blocks,
+                         int32_t heads, const int32_t* indices, const int32_t* counts, int64_t index_head_stride,
+                         int64_t count_head_stride, int32_t capacity, const int32_t* kv_sizes, float scale,
+                         void* o_slots, float* lse, const int64_t* slot_row, const int32_t* block_coarse,
+                         const void* gate, int64_t gate_row_stride, int64_t gate_head_stride, const void* coarse,
+                         void* out, int64_t out_rows, int32_t* status, void* stream) {
+  if (o_slots == nullptr) return vsa::kBadArgument;
+  return fine_fwd_common(q, k, v, q_blocks, kv_blocks, heads, indices, counts, index_head_stride, count_head_stride,
+                         capacity, kv_sizes, scale, o_slots, lse, nullptr, slot_row, block_coarse, gate,
+                         gate_row_stride, gate_head_stride, coarse, out, out_rows, status, stream);
 }
 
 int vsa_fine_fwd_running(const void* q, const void* k, const void* v, int64_t q_blocks, int64_t kv_blocks,
@@ -192,18 +245,28 @@ int vsa_fine_fwd_running(const void* q, const void* k, const void* v, int64_t q_
                          float* o_running, float* lse_running, int32_t* status, void* stream) {
   if (o_running == nullptr) return vsa::kBadArgument;
   return fine_fwd_common(q, k, v, q_blocks, kv_blocks, heads, indices, counts, index_head_stride, count_head_stride,
-                         capacity, kv_sizes, scale, nullptr, lse_running, o_running, nullptr, nullptr, nullptr, nullptr,
-                         nullptr, 0, status, stream);
+                         capacity, kv_sizes, scale, nullptr, lse_running, o_running, nullptr, nullptr, nullptr, 0, 0,
+                         nullptr, nullptr, 0, status, stream);
 }
 
-int vsa_merge_bwd(const void* grad, const void* gate, const void* coarse, const void* o_slots, const int64_t* slot_row,
-                  const int32_t* block_coarse, void* grad_slots, void* dgate, void* dcoarse, float* delta,
-                  float* coarse_delta, int64_t blocks, int64_t coarse_rows, int32_t heads, void* stream) {
+}  // extern "C" (reopened below)
+
+namespace {
+
+int merge_bwd_common(const void* grad, const void* gate, int64_t io_row_stride, int64_t io_head_stride,
+                     const void* coarse, const void* o_slots, const int64_t* slot_row, const int32_t* block_coarse,
+                     void* grad_slots, void* dgate, void* dcoarse, float* delta, float* coarse_delta, int64_t blocks,
+                     int64_t coarse_rows, int32_t heads, void* stream) {
   if (grad == nullptr || o_slots == nullptr || delta == nullptr || blocks < 0 || heads <= 0) return vsa::kBadArgument;
   if (coarse != nullptr && (gate == nullptr || block_coarse == nullptr)) return vsa::kBadArgument;
+  if (bad_strides(io_row_stride, io_head_stride, heads) ||
+      ((reinterpret_cast<uintptr_t>(gate) | reinterpret_cast<uintptr_t>(dgate)) & 15) != 0)
+    return vsa::kBadArgument;
   vsa::MergeBwdParams p{};
   p.grad = static_cast<const __nv_bfloat16*>(grad);
   p.gate = static_cast<const __nv_bfloat16*>(gate);
+  p.io_row_stride = io_row_stride;
+  p.io_head_stride = io_head_stride;
   p.coarse = static_cast<const __nv_bfloat16*>(coarse);
   p.o_slots = static_cast<const __nv_bfloat16*>(o_slots);
   p.slot_row = slot_row;
@@ -219,16 +282,42 @@ int vsa_merge_bwd(const void* grad, const void* gate, const void* coarse, const 
   return from_cuda(vsa::launch_merge_bwd(p, as_stream(stream)));
 }
 
+}  // namespace
+
+extern "C" {
+
+int vsa_merge_bwd(const void* grad, const void* gate, const void* coarse, const void* o_slots, const int64_t* slot_row,
+                  const int32_t* block_coarse, void* grad_slots, void* dgate, void* dcoarse, float* delta,
+                  float* coarse_delta, int64_t blocks, int64_t coarse_rows, int32_t heads, void* stream) {
+  return merge_bwd_common(grad, gate, static_cast<int64_t>(heads) * vsa::kDim, vsa::kDim, coarse, o_slots, slot_row,
+                          block_coarse, grad_slots, dgate, dcoarse, delta, coarse_delta, blocks, coarse_rows, heads,
+                          stream);
+}
+
+int vsa_merge_bwd_strided(const void* grad, const void* gate, int64_t io_row_stride, int64_t io_head_stride,
+                          const void* coarse, const void* o_slots, const int64_t* slot_row,
+                          const int32_t* block_coarse, void* grad_slots, void* dgate, void* dcoarse, float* delta,
+                          float* coarse_delta, int64_t blocks, int64_t coarse_rows, int32_t heads, void* stream) {
+  return merge_bwd_common(grad, gate, io_row_stride, io_head_stride, coarse, o_slots, slot_row, block_coarse,
+                          grad_slots, dgate, dcoarse, delta, coarse_delta, blocks, coarse_rows, heads, stream);
+}
+
 int64_t vsa_kv_mask_words(int64_t q_blocks) { return (q_blocks + 31) / 32; }
 
-int vsa_fine_bwd(const void* q, const void* k, const void* v, const void* d_o, int64_t q_blocks, int64_t kv_blocks,
-                 int32_t heads, const int32_t* indices, const int32_t* counts, int64_t index_head_stride,
-                 int64_t count_head_stride, int32_t capacity, const int32_t* q_sizes, const int32_t* kv_sizes,
-                 float scale, const float* lse, const float* delta, uint32_t* kv_mask, void* dq, void* dk, void* dv,
-                 int64_t q_out_rows, int64_t kv_out_rows, const int64_t* q_slot_row, const int64_t* kv_slot_row,
-                 const void* dq_pool, const void* dk_pool, const void* dv_pool, int32_t pool_f32,
-                 const int32_t* q_block_coarse, const int32_t* kv_block_coarse, float* dq_f32, float* dk_f32,
-                 float* dv_f32, int32_t f32_accumulate, int32_t parts, int32_t* status, void* stream) {
+}  // extern "C" (reopened below)
+
+namespace {
+
+int fine_bwd_common(const void* q, const void* k, const void* v, const void* d_o, int64_t q_blocks, int64_t kv_blocks,
+                    int32_t heads, const int32_t* indices, const int32_t* counts, int64_t index_head_stride,
+                    int64_t count_head_stride, int32_t capacity, const int32_t* q_sizes, const int32_t* kv_sizes,
+                    float scale, const float* lse, const float* delta, uint32_t* kv_mask, void* dq, void* dk, void* dv,
+                    int64_t out_row_stride, int64_t out_head_stride, int64_t q_out_rows, int64_t kv_out_rows,
+                    const int64_t* q_slot_row, const int64_t* kv_slot_row, const void* dq_pool, const void* dk_pool,
+                    const void* dv_pool, int32_t pool_f32, const int32_t* q_block_coarse,
+                    const int32_t* kv_block_coarse, float* dq_f32, float* dk_f32, float* dv_f32,
+                    int32_t f32_accumulate, int32_t parts, int32_t* status, void* stream) {
+  if (out_row_stride < static_cast<int64_t>(heads) * vsa::kDim || out_head_stride < vsa::kDim) return vsa::kBadArgument;
   if (q == nullptr || k == nullptr || v == nullptr || d_o == nullptr || indices == nullptr || counts == nullptr ||
       lse == nullptr || delta == nullptr || kv_mask == nullptr || q_blocks <= 0 || kv_blocks <= 0 || heads <= 0 ||
       capacity <= 0)
@@ -263,6 +352,8 @@ int vsa_fine_bwd(const void* q, const void* k, const void* v, const void* d_o, i
   p.dq = static_cast<__nv_bfloat16*>(dq);
   p.dk = static_cast<__nv_bfloat16*>(dk);
   p.dv = static_cast<__nv_bfloat16*>(dv);
+  p.out_row_stride = out_row_stride;
+  p.out_head_stride = out_head_stride;
   p.q_slot_row = q_slot_row;
   p.kv_slot_row = kv_slot_row;
   p.dq_pool = dq_pool;
@@ -295,6 +386,41 @@ int vsa_fine_bwd(const void* q, const void* k, const void* v, const void* d_o, i
   if (err == cudaSuccess && (parts & 2)) err = vsa::launch_fine_bwd_dq(p, s);
   if (err == cudaSuccess && (parts & 4)) err = vsa::launch_fine_bwd_dkv(p, s);
   return from_cuda(err);
+}
+
+}  // namespace
+
+extern "C" {
+
+int vsa_fine_bwd(const void* q, const void* k, const void* v, const void* d_o, int64_t q_blocks, int64_t kv_blocks,
+                 int32_t heads, const int32_t* indices, const int32_t* counts, int64_t index_head_stride,
+                 int64_t count_head_stride, int32_t capacity, const int32_t* q_sizes, const int32_t* kv_sizes,
+                 float scale, const float* lse, const float* delta, uint32_t* kv_mask, void* dq, void* dk, void* dv,
+                 int64_t q_out_rows, int64_t kv_out_rows, const int64_t* q_slot_row, const int64_t* kv_slot_row,
+                 const void* dq_pool, const void* dk_pool, const void* dv_pool, int32_t pool_f32,
+                 const int32_t* q_block_coarse, const int32_t* kv_block_coarse, float* dq_f32, float* dk_f32,
+                 float* dv_f32, int32_t f32_accumulate, int32_t parts, int32_t* status, void* stream) {
+  return fine_bwd_common(q, k, v, d_o, q_blocks, kv_blocks, heads, indices, counts, index_head_stride,
+                         count_head_stride, capacity, q_sizes, kv_sizes, scale, lse, delta, kv_mask, dq, dk, dv,
+                         static_cast<int64_t>(heads) * vsa::kDim, vsa::kDim, q_out_rows, kv_out_rows, q_slot_row,
+                         kv_slot_row, dq_pool, dk_pool, dv_pool, pool_f32, q_block_coarse, kv_block_coarse, dq_f32,
+                         dk_f32, dv_f32, f32_accumulate, parts, status, stream);
+}
+
+int vsa_fine_bwd_strided(const void* q, const void* k, const void* v, const void* d_o, int64_t q_blocks,
+                         int64_t kv_blocks, int32_t heads, const int32_t* indices, const int32_t* counts,
+                         int64_t index_head_stride, int64_t count_head_stride, int32_t capacity,
+                         const int32_t* q_sizes, const int32_t* kv_sizes, float scale, const float* lse,
+                         const float* delta, uint32_t* kv_mask, void* dq, void* dk, void* dv, int64_t out_row_stride,
+                         int64_t out_head_stride, int64_t q_out_rows, int64_t kv_out_rows, const int64_t* q_slot_row,
+                         const int64_t* kv_slot_row, const void* dq_pool, const void* dk_pool, const void* dv_pool,
+                         int32_t pool_f32, const int32_t* q_block_coarse, const int32_t* kv_block_coarse,
+                         int32_t parts, int32_t* status, void* stream) {
+  return fine_bwd_common(q, k, v, d_o, q_blocks, kv_blocks, heads, indices, counts, index_head_stride,
+                         count_head_stride, capacity, q_sizes, kv_sizes, scale, lse, delta, kv_mask, dq, dk, dv,
+                         out_row_stride, out_head_stride, q_out_rows, kv_out_rows, q_slot_row, kv_slot_row, dq_pool,
+                         dk_pool, dv_pool, pool_f32, q_block_coarse, kv_block_coarse, nullptr, nullptr, nullptr, 0,
+                         parts, status, stream);
 }
 
 int vsa_partition_indices(const int32_t* index, const int32_t* counts, const int64_t* global_to_gather,

@@ -25,12 +25,14 @@ namespace {
 // slots of `block`, of which the first `valid` are real and the first `computed` (a multiple of 16)
 // were produced by the products.  Adds `term` and writes BF16 to the mapped rows of `out`, or FP32
 // in slot order (added to the buffer's content when `accumulate`); padding slots are left alone.
+// BF16 element (row, this thread's head and dim) sits at row * out_row_stride + out_col.
 // A warp store covers 32 consecutive elements of one row.  The FP32 read-modify-write fetches a
 // whole chunk of old values before it stores any, so the loads are in flight together instead
 // of each waiting behind the previous store.
 VSA_DEVICE void store_grad_columns(bool have_acc, uint32_t tmem_addr, float term, const long long* out_rows,
-                                   long long out_limit, __nv_bfloat16* out, float* out_f32, bool accumulate,
-                                   long long block, long long width, long long col, int valid, int computed) {
+                                   long long out_limit, __nv_bfloat16* out, long long out_row_stride,
+                                   long long out_col, float* out_f32, bool accumulate, long long block,
+                                   long long width, long long col, int valid, int computed) {
 #pragma unroll
   for (int c = 0; c < 2; ++c) {
     if (c * 32 >= valid) break;
@@ -53,7 +55,7 @@ VSA_DEVICE void store_grad_columns(bool have_acc, uint32_t tmem_addr, float term
         const int r = c * 32 + i;
         const long long row = out_rows[r];
         if (r < valid && row >= 0 && row < out_limit)
-          out[row * width + col] = __float2bfloat16(__uint_as_float(bits[i]) + term);
+          out[row * out_row_stride + out_col] = __float2bfloat16(__uint_as_float(bits[i]) + term);
       }
     }
   }
@@ -384,14 +386,15 @@ __global__ void __launch_bounds__(kDkvThreads, 1) fine_bwd_dkv_kernel(const __gr
     // Thread = head dim `qrow`; warpgroup 0 writes dK, warpgroup 1 writes dV.
     const long long width = static_cast<long long>(p.heads) * kDim;
     const long long col = static_cast<long long>(head) * kDim + qrow;
+    const long long out_col = static_cast<long long>(head) * p.out_head_stride + qrow;
     if (group == 0) {
       const float term = pool_term(p.dk_pool, p.pool_f32, p.kv_block_coarse, kvb, kv_size, width, col);
-      store_grad_columns(n > 0, tmem + lane_base + kColDk, term, sm.out_row, p.kv_out_rows, p.dk, p.dk_f32,
-                         p.f32_accumulate != 0, kvb, width, col, kv_size, kv_n);
+      store_grad_columns(n > 0, tmem + lane_base + kColDk, term, sm.out_row, p.kv_out_rows, p.dk, p.out_row_stride,
+                         out_col, p.dk_f32, p.f32_accumulate != 0, kvb, width, col, kv_size, kv_n);
     } else {
       const float term = pool_term(p.dv_pool, p.pool_f32, p.kv_block_coarse, kvb, kv_size, width, col);
-      store_grad_columns(n > 0, tmem + lane_base + kColDv, term, sm.out_row, p.kv_out_rows, p.dv, p.dv_f32,
-                         p.f32_accumulate != 0, kvb, width, col, kv_size, kv_n);
+      store_grad_columns(n > 0, tmem + lane_base + kColDv, term, sm.out_row, p.kv_out_rows, p.dv, p.out_row_stride,
+                         out_col, p.dv_f32, p.f32_accumulate != 0, kvb, width, col, kv_size, kv_n);
     }
   }
   tc_fence_before();

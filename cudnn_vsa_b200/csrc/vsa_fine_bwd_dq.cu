@@ -363,7 +363,7 @@ __global__ void __launch_bounds__(kThreads, 1) fine_bwd_dq_kernel(const __grid_c
           const int r = group * 32 + i;
           const long long row = sm.out_row[r];
           if (r < q_size && row >= 0 && row < p.q_out_rows)
-            p.dq[row * width + col] = __float2bfloat16(__uint_as_float(bits[i]) + term);
+            p.dq[row * p.out_row_stride + head * p.out_head_stride + key] = __float2bfloat16(__uint_as_float(bits[i]) + term);
         }
       }
     }

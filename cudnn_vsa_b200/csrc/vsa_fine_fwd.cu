@@ -409,7 +409,7 @@ __global__ void __launch_bounds__(kThreads, 1) fine_fwd_kernel(const __grid_cons
         if (out_row >= p.out_rows) out_row = -1;
         const int coarse_slot = p.block_coarse != nullptr ? p.block_coarse[qb] : -1;
         if (coarse_slot >= 0 && out_row >= 0) {
-          gate = reinterpret_cast<const uint4*>(p.gate + out_row * width + col);
+          gate = reinterpret_cast<const uint4*>(p.gate + out_row * p.gate_row_stride + head * p.gate_head_stride + dim0);
           coarse = reinterpret_cast<const uint4*>(p.coarse + coarse_slot * width + col);
         }
       }

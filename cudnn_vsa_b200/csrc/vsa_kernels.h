@@ -26,7 +26,8 @@ struct FineFwdParams {
   // merged output in caller row order (kMerge only)
   const int64_t* slot_row;          // [q_slots] caller row per slot (-1 = padding), null = identity
   const int32_t* block_coarse;      // [q_blocks] coarse row of each query block (-1 = none), or null
-  const __nv_bfloat16* gate;        // [out_rows, heads, 128]
+  const __nv_bfloat16* gate;        // [out_rows, heads, 128]; element (row, head, d) at row * gate_row_stride + head * gate_head_stride + d
+  long long gate_row_stride, gate_head_stride;
   const __nv_bfloat16* coarse;      // [coarse_rows, heads, 128]
   __nv_bfloat16* out;               // [out_rows, heads, 128]
   long long out_rows;
@@ -54,6 +55,9 @@ struct FineBwdParams {
   __nv_bfloat16* dq;            // [q_out_rows, heads, 128]
   __nv_bfloat16* dk;            // [kv_out_rows, heads, 128]
   __nv_bfloat16* dv;
+  // Element (row, head, d) of dq / dk / dv sits at row * out_row_stride + head * out_head_stride + d
+  // (heads * 128 and 128 for contiguous tensors; other values write into an interleaved buffer).
+  long long out_row_stride, out_head_stride;
   const int64_t* q_slot_row;    // [q_slots] caller row per slot (-1 = padding) or null (identity)
   const int64_t* kv_slot_row;   // [kv_slots] or null
   // Gradient of the pooled block means, added as pool[block] / max(size, 1) to every valid row.
@@ -99,6 +103,8 @@ struct PoolParams {
   const __nv_bfloat16* q;   // [rows, width] caller order (width = heads * 128)
   const __nv_bfloat16* k;
   const __nv_bfloat16* v;
+  // Element (row, head, d) of q / k / v sits at row * in_row_stride + head * in_head_stride + d.
+  long long in_row_stride, in_head_stride;
   const int64_t* slot_row;  // [blocks * 64] or null when the inputs already are the slots
   const int32_t* sizes;     // [blocks]
   __nv_bfloat16* q_slots;   // [blocks * 64, width] or null (no slot copy wanted)
@@ -132,6 +138,8 @@ cudaError_t launch_route_chunk(const float* q_mean, const float* k_mean, int hea
 struct MergeBwdParams {
   const __nv_bfloat16* grad;     // [rows, width] dO in caller order
   const __nv_bfloat16* gate;     // [rows, width] or null
+  // Element (row, head, d) of gate and dgate sits at row * io_row_stride + head * io_head_stride + d.
+  long long io_row_stride, io_head_stride;
   const __nv_bfloat16* coarse;   // [coarse_rows, width] or null
   const __nv_bfloat16* o_slots;  // [blocks * 64, width] fine output saved by the forward pass
   const int64_t* slot_row;       // [blocks * 64] or null (identity)

@@ -67,6 +67,9 @@ __global__ void __launch_bounds__(kCtaThreads) slots_pool_kernel(const PoolParam
   uint4* dst[3] = {reinterpret_cast<uint4*>(p.q_slots), reinterpret_cast<uint4*>(p.k_slots),
                    reinterpret_cast<uint4*>(p.v_slots)};
   float acc[3][8] = {};
+  // Input rows may be strided (q, k, v interleaved in one projection output): 16-byte units.
+  const long long in_row = p.in_row_stride / kChunk;
+  const long long in_col = (c / (kDim / kChunk)) * (p.in_head_stride / kChunk) + c % (kDim / kChunk);
   if (active) {
 #pragma unroll 8
     for (int s = group * per; s < (group + 1) * per; ++s) {
@@ -75,7 +78,7 @@ __global__ void __launch_bounds__(kCtaThreads) slots_pool_kernel(const PoolParam
 #pragma unroll
       for (int t = 0; t < 3; ++t) {
         uint4 v = make_uint4(0, 0, 0, 0);
-        if (row >= 0) v = __ldg(src[t] + row * chunks + c);
+        if (row >= 0) v = __ldg(src[t] + row * in_row + in_col);
         if (dst[t] != nullptr) dst[t][out] = v;
         accumulate(acc[t], v);
       }
@@ -152,6 +155,9 @@ __global__ void __launch_bounds__(kCtaThreads) merge_bwd_kernel(const MergeBwdPa
   const uint4* fine = reinterpret_cast<const uint4*>(p.o_slots);
   float cz[8] = {};
   if (active && coarse_row >= 0) accumulate(cz, __ldg(reinterpret_cast<const uint4*>(p.coarse) + coarse_row * chunks + c));
+  // gate and dgate rows may be strided (one field of an interleaved tensor): 16-byte units.
+  const long long io_row = p.io_row_stride / kChunk;
+  const long long io_col = (c / (kDim / kChunk)) * (p.io_head_stride / kChunk) + c % (kDim / kChunk);
   float dc[8] = {};
 #pragma unroll 2
   for (int s = group * per; s < (group + 1) * per; ++s) {
@@ -163,7 +169,7 @@ __global__ void __launch_bounds__(kCtaThreads) merge_bwd_kernel(const MergeBwdPa
       gv = __ldg(grad + row * chunks + c);
       const uint4 ov = __ldg(fine + slot * chunks + c);
       uint4 tv = make_uint4(0, 0, 0, 0);
-      if (coarse_row >= 0) tv = __ldg(gate + row * chunks + c);
+      if (coarse_row >= 0) tv = __ldg(gate + row * io_row + io_col);
       accumulate(g, gv);
       accumulate(o, ov);
       if (coarse_row >= 0) {
@@ -176,11 +182,11 @@ __global__ void __launch_bounds__(kCtaThreads) merge_bwd_kernel(const MergeBwdPa
           dc[e] += g[e] * gt[e];
         }
         if (p.dgate != nullptr)
-          reinterpret_cast<uint4*>(p.dgate)[row * chunks + c] =
+          reinterpret_cast<uint4*>(p.dgate)[row * io_row + io_col] =
               make_uint4(pack_bf16(dg[0], dg[1]), pack_bf16(dg[2], dg[3]), pack_bf16(dg[4], dg[5]),
                          pack_bf16(dg[6], dg[7]));
       } else if (p.dgate != nullptr) {
-        reinterpret_cast<uint4*>(p.dgate)[row * chunks + c] = make_uint4(0, 0, 0, 0);
+        reinterpret_cast<uint4*>(p.dgate)[row * io_row + io_col] = make_uint4(0, 0, 0, 0);
       }
     }
     if (active && p.grad_slots != nullptr) reinterpret_cast<uint4*>(p.grad_slots)[slot * chunks + c] = gv;

@@ -320,6 +320,108 @@ class _VSAFunction(torch.autograd.Function):
         return dq, dk, dv, dgate, None, None
 
 
+def _field(mixed, n):
+    """Device address of field ``n`` (0..3 = q, k, v, gate) of an interleaved ``[T, H, 4, D]`` tensor."""
+    from ctypes import c_void_p
+    return c_void_p(mixed.data_ptr() + n * mixed.shape[3] * mixed.element_size())
+
+
+class _VSAFusedFunction(torch.autograd.Function):
+    """Single-device VSA on an interleaved ``[T, H, 4, 128]`` projection output (q, k, v, gate per
+    head).  The slot gather reads q, k and v straight out of it, the merge epilogue and its
+    adjoint read the gate field in place, and the backward kernels write dq, dk, dv and dgate
+    into the four fields of ONE gradient tensor: no ``.contiguous()`` of the four projections
+    before the call and no concatenation of four gradients after it (the reference requires
+    materialised contiguous inputs, ``vsa.py:50-61``).  Same kernels and arithmetic as
+    :class:`_VSAFunction`, so results are bit-identical to the unfused call."""
+
+    @staticmethod
+    def forward(ctx, mixed, layout, scale):
+        plan = device_plan(layout)
+        tokens, heads, _, dim = mixed.shape
+        blocks = layout.blocks
+        row_stride, head_stride = heads * 4 * dim, 4 * dim
+        coarse = plan.coarse
+        need_means = bool(plan.spans)
+        mean_f32 = (torch.empty((3, blocks, heads, dim), dtype=torch.float32, device=mixed.device)
+                    if need_means else None)
+        tokens_bf16 = (torch.zeros((3, coarse.q_rows, heads, dim), dtype=mixed.dtype, device=mixed.device)
+                       if coarse is not None else None)
+        q_s, k_s, v_s = (torch.empty((blocks * BLOCK, heads, dim), dtype=mixed.dtype, device=mixed.device)
+                         for _ in range(3))
+        slot_row = None if layout.slots_are_input else layout.slot_row
+        _cabi.call("vsa_slots_pool_strided", _field(mixed, 0), _field(mixed, 1), _field(mixed, 2), row_stride,
+                   head_stride, _p(slot_row), _p(layout.block_sizes), _p(q_s), _p(k_s), _p(v_s), _p(mean_f32),
+                   _p(coarse.block_q) if coarse is not None else None, _p(tokens_bf16),
+                   coarse.q_rows if coarse is not None else 0, blocks, heads, _cabi.stream())
+        index = route(mean_f32[0], mean_f32[1], layout, plan) if need_means else layout.routing_indices
+        coarse_o = coarse_lse = None
+        if coarse is not None:
+            coarse_o, coarse_lse = _fine_fwd(tokens_bf16[0], tokens_bf16[1], tokens_bf16[2], coarse.index,
+                                             coarse.counts, (0, 0), coarse.kv_sizes, scale, plan.status)
+        counts = layout.routing_counts
+        o_s = torch.empty_like(q_s)
+        lse = torch.empty((heads, blocks * BLOCK), dtype=torch.float32, device=mixed.device)
+        out = torch.empty((tokens, heads, dim), dtype=mixed.dtype, device=mixed.device)
+        _cabi.call("vsa_fine_fwd_strided", _p(q_s), _p(k_s), _p(v_s), blocks, blocks, heads, _p(index), _p(counts),
+                   index.stride(1), counts.stride(1), index.shape[-1], _p(plan.sizes), scale, _p(o_s), _p(lse),
+                   _p(slot_row), _p(coarse.block_q) if coarse is not None else None,
+                   _field(mixed, 3) if coarse is not None else None, row_stride, head_stride, _p(coarse_o), _p(out),
+                   tokens, _p(plan.status), _cabi.stream())
+        ctx.save_for_backward(mixed, q_s, k_s, v_s, o_s, lse, index, tokens_bf16, coarse_o, coarse_lse)
+        ctx.layout, ctx.scale = layout, scale
+        return out
+
+    @staticmethod
+    def backward(ctx, grad):
+        mixed, q_s, k_s, v_s, o_s, lse, index, tokens_bf16, coarse_o, coarse_lse = ctx.saved_tensors
+        layout, scale = ctx.layout, ctx.scale
+        plan = device_plan(layout)
+        coarse = plan.coarse
+        grad = grad.contiguous()
+        tokens, heads, dim = grad.shape
+        blocks = layout.blocks
+        row_stride, head_stride = heads * 4 * dim, 4 * dim
+        slot_row = None if layout.slots_are_input else layout.slot_row
+        d_mixed = torch.empty_like(mixed)
+        grad_s = torch.empty_like(q_s)
+        delta = torch.empty((heads, blocks * BLOCK), dtype=torch.float32, device=grad.device)
+        dcoarse = coarse_delta = None
+        if coarse is not None:
+            dcoarse = torch.zeros_like(coarse_o)
+            coarse_delta = torch.zeros((heads, coarse.q_rows), dtype=torch.float32, device=grad.device)
+        else:
+            d_mixed[:, :, 3].zero_()  # a pack without coarse attention has no gate gradient
+        _cabi.call("vsa_merge_bwd_strided", _p(grad), _field(mixed, 3) if coarse is not None else None, row_stride,
+                   head_stride, _p(coarse_o), _p(o_s), _p(slot_row),
+                   _p(coarse.block_q) if coarse is not None else None, _p(grad_s),
+                   _field(d_mixed, 3) if coarse is not None else None, _p(dcoarse), _p(delta), _p(coarse_delta),
+                   blocks, coarse.q_rows if coarse is not None else 0, heads, _cabi.stream())
+        pools = (None, None, None)
+        if coarse is not None:
+            pools = _fine_bwd(tokens_bf16[0], tokens_bf16[1], tokens_bf16[2], dcoarse, coarse.index,
+                              coarse.counts, (0, 0), coarse.q_sizes, coarse.kv_sizes, scale, coarse_lse,
+                              coarse_delta, plan.status)
+        counts = layout.routing_counts
+        words = _cabi.load().vsa_kv_mask_words(blocks)
+        mask = torch.empty(heads * blocks * words, dtype=torch.int32, device=grad.device)
+        block_coarse = coarse.block_q if coarse is not None else None
+        _cabi.call("vsa_fine_bwd_strided", _p(q_s), _p(k_s), _p(v_s), _p(grad_s), blocks, blocks, heads, _p(index),
+                   _p(counts), index.stride(1), counts.stride(1), index.shape[-1], _p(layout.block_sizes),
+                   _p(plan.sizes), scale, _p(lse), _p(delta), _p(mask), _field(d_mixed, 0), _field(d_mixed, 1),
+                   _field(d_mixed, 2), row_stride, head_stride, tokens, tokens, _p(slot_row), _p(slot_row),
+                   _p(pools[0]), _p(pools[1]), _p(pools[2]), 0, _p(block_coarse), _p(block_coarse), 7,
+                   _p(plan.status), _cabi.stream(), launches=3)
+        return d_mixed, None, None
+
+
+def attention_fused(mixed, layout, *, scale=None):
+    """Single-device packed VSA on validated interleaved inputs; see
+    :func:`cudnn_vsa_b200.vsa.vsa_attention_fused`."""
+    scale = mixed.shape[-1] ** -0.5 if scale is None else float(scale)
+    return _VSAFusedFunction.apply(mixed, layout, scale)
+
+
 def attention(q, k, v, gate, layout, *, scale=None):
     """Single-device packed VSA on validated inputs; see :func:`cudnn_vsa_b200.vsa.vsa_attention`."""
     scale = q.shape[-1] ** -0.5 if scale is None else float(scale)

@@ -59,6 +59,17 @@ int vsa_slots_pool(const void* q, const void* k, const void* v, const int64_t* s
                    void* q_slots, void* k_slots, void* v_slots, float* mean_f32, const int32_t* block_coarse,
                    void* mean_bf16, int64_t coarse_rows, int64_t blocks, int32_t heads, void* stream);
 
+/* vsa_slots_pool for q, k, v that are fields of one interleaved tensor, e.g. the caller's fused
+ * QKV + gate projection output viewed as [rows, heads, 4, 128]: element (row, head, d) of each
+ * input sits at row * in_row_stride + head * in_head_stride + d (in elements, multiples of 8;
+ * heads * 128 and 128 describe a contiguous tensor).  The slot tensors and means it writes are
+ * contiguous as always.  Relaxes the materialised-input contract of vsa.py:50-61: the
+ * `.contiguous()` copies of q, k and v that precede the reference's slot gather disappear. */
+int vsa_slots_pool_strided(const void* q, const void* k, const void* v, int64_t in_row_stride, int64_t in_head_stride,
+                           const int64_t* slot_row, const int32_t* block_sizes, void* q_slots, void* k_slots,
+                           void* v_slots, float* mean_f32, const int32_t* block_coarse, void* mean_bf16,
+                           int64_t coarse_rows, int64_t blocks, int32_t heads, void* stream);
+
 /* Bytes of `scratch` that vsa_route needs for a region of `rows` query blocks x `region` KV
  * blocks when it may process `heads` heads at once (it processes fewer per pass if given less). */
 int64_t vsa_route_scratch_bytes(int64_t rows, int64_t region, int32_t heads);
@@ -114,6 +125,15 @@ int vsa_fine_fwd(const void* q, const void* k, const void* v, int64_t q_blocks, 
                  const int64_t* slot_row, const int32_t* block_coarse, const void* gate, const void* coarse,
                  void* out, int64_t out_rows, int32_t* status, void* stream);
 
+/* vsa_fine_fwd with a strided gate: element (row, head, d) of `gate` sits at
+ * row * gate_row_stride + head * gate_head_stride + d (the gate field of an interleaved tensor). */
+int vsa_fine_fwd_strided(const void* q, const void* k, const void* v, int64_t q_blocks, int64_t kv_blocks,
+                         int32_t heads, const int32_t* indices, const int32_t* counts, int64_t index_head_stride,
+                         int64_t count_head_stride, int32_t capacity, const int32_t* kv_sizes, float scale,
+                         void* o_slots, float* lse, const int64_t* slot_row, const int32_t* block_coarse,
+                         const void* gate, int64_t gate_row_stride, int64_t gate_head_stride, const void* coarse,
+                         void* out, int64_t out_rows, int32_t* status, void* stream);
+
 /* Ring step of the forward pass: vsa_fine_fwd on the shard that is here, with the online-softmax
  * merge into the running result done in the kernel's epilogue.  o_running [q_blocks*64, heads, 128]
  * FP32 holds the normalised result of the steps so far (zero before the first) and lse_running
@@ -135,6 +155,13 @@ int vsa_fine_fwd_running(const void* q, const void* k, const void* v, int64_t q_
 int vsa_merge_bwd(const void* grad, const void* gate, const void* coarse, const void* o_slots, const int64_t* slot_row,
                   const int32_t* block_coarse, void* grad_slots, void* dgate, void* dcoarse, float* delta,
                   float* coarse_delta, int64_t blocks, int64_t coarse_rows, int32_t heads, void* stream);
+
+/* vsa_merge_bwd with strided gate and dgate (both with the same strides: the gate field of an
+ * interleaved activation tensor and the same field of its gradient). */
+int vsa_merge_bwd_strided(const void* grad, const void* gate, int64_t io_row_stride, int64_t io_head_stride,
+                          const void* coarse, const void* o_slots, const int64_t* slot_row,
+                          const int32_t* block_coarse, void* grad_slots, void* dgate, void* dcoarse, float* delta,
+                          float* coarse_delta, int64_t blocks, int64_t coarse_rows, int32_t heads, void* stream);
 
 /* Words per (head, KV block) row of the query-block bitmask used by vsa_fine_bwd. */
 int64_t vsa_kv_mask_words(int64_t q_blocks);
@@ -165,6 +192,19 @@ int vsa_fine_bwd(const void* q, const void* k, const void* v, const void* d_o, i
                  const void* dq_pool, const void* dk_pool, const void* dv_pool, int32_t pool_f32,
                  const int32_t* q_block_coarse, const int32_t* kv_block_coarse, float* dq_f32, float* dk_f32,
                  float* dv_f32, int32_t f32_accumulate, int32_t parts, int32_t* status, void* stream);
+
+/* vsa_fine_bwd writing BF16 dq / dk / dv rows with strides: element (row, head, d) goes to
+ * row * out_row_stride + head * out_head_stride + d of each output (the q, k, v fields of the
+ * gradient of an interleaved projection output, so no concatenation follows).  BF16 outputs only. */
+int vsa_fine_bwd_strided(const void* q, const void* k, const void* v, const void* d_o, int64_t q_blocks,
+                         int64_t kv_blocks, int32_t heads, const int32_t* indices, const int32_t* counts,
+                         int64_t index_head_stride, int64_t count_head_stride, int32_t capacity,
+                         const int32_t* q_sizes, const int32_t* kv_sizes, float scale, const float* lse,
+                         const float* delta, uint32_t* kv_mask, void* dq, void* dk, void* dv, int64_t out_row_stride,
+                         int64_t out_head_stride, int64_t q_out_rows, int64_t kv_out_rows, const int64_t* q_slot_row,
+                         const int64_t* kv_slot_row, const void* dq_pool, const void* dk_pool, const void* dv_pool,
+                         int32_t pool_f32, const int32_t* q_block_coarse, const int32_t* kv_block_coarse,
+                         int32_t parts, int32_t* status, void* stream);
 
 /* Ring: split routing rows into per-owner lists of owner-local block ids.
  *   index [rows, capacity], counts [rows], global_to_gather [global blocks] int64.

@@ -282,3 +282,30 @@ def test_retained_graph_second_backward_is_identical():
     second = torch.autograd.grad(out, leaves, dy)
     for a, b in zip(first, second):
         assert torch.equal(a, b)
+
+
+@pytest.mark.parametrize("name,order", [("ragged", "raster"), ("mixed", "block"), ("full_blocks", "block"),
+                                        ("dense", "raster"), ("c1", "raster")])
+def test_fused_projection_input_is_bit_identical_to_separate_tensors(name, order):
+    """``vsa_attention_fused`` on one interleaved [T, H, 4, 128] tensor against ``vsa_attention`` on
+    its four contiguous fields: same kernels, strided reads and writes - output and the gradient
+    of the interleaved tensor must match bit for bit."""
+    from cudnn_vsa_b200.vsa import vsa_attention_fused
+    heads = 3
+    layout = build_vsa_layout(GEOMETRIES[name], head_num=heads, device="cuda", input_order=order)
+    gen = torch.Generator(device="cuda").manual_seed(3)
+    mixed = torch.randn(layout.tokens, heads, 4, 128, device="cuda", dtype=torch.bfloat16, generator=gen)
+    dy = torch.randn(layout.tokens, heads, 128, device="cuda", dtype=torch.bfloat16, generator=gen)
+    fused_in = mixed.clone().requires_grad_()
+    out = vsa_attention_fused(fused_in, layout)
+    grad, = torch.autograd.grad(out, fused_in, dy)
+    ref_in = mixed.clone().requires_grad_()
+    ref_out = vsa_attention(*(t.contiguous() for t in ref_in.unbind(2)), layout)
+    ref_grad, = torch.autograd.grad(ref_out, ref_in, dy)
+    vsa_core.check_status(layout)
+    assert torch.equal(out, ref_out)
+    assert torch.equal(grad, ref_grad)
+    with pytest.raises(ValueError, match="contiguous"):
+        vsa_attention_fused(mixed.transpose(0, 1).contiguous().transpose(0, 1), layout)
+    with pytest.raises(ValueError, match="4, head_dim"):
+        vsa_attention_fused(mixed[:, :, :3].contiguous(), layout)
