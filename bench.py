@@ -160,12 +160,12 @@ class CpuSample:
                           for x in self.slots[:2]]
         self.order = torch.randperm(layout.blocks, generator=torch.Generator().manual_seed(seed + 1))
 
-    def run(self, seconds, chunk=16):
+    def run(self, seconds, chunk=None):
         """One pass: returns (useful FLOPs done, seconds spent, query blocks done)."""
         layout, oracle = self.layout, self.oracle
+        chunk = chunk or (16 if layout.blocks <= 4096 else 4)
         sizes = layout.block_sizes.double()
         offsets = torch.arange(BLOCK)
-        k_all, v_all = (x.clone().requires_grad_() for x in self.slots[1:])
         done_blocks, pairs = 0, 0.0
         start = time.perf_counter()
         while done_blocks < layout.blocks and (done_blocks == 0 or time.perf_counter() - start < seconds):
@@ -173,11 +173,18 @@ class CpuSample:
             index = (oracle.route(self.means[0], self.means[1], layout, query_blocks=picked)
                      if self.means is not None else layout.routing_indices[:, :, picked].contiguous())
             counts = layout.routing_counts[:, :, picked].contiguous()
+            valid = torch.arange(index.shape[-1]) < counts[0][..., None]
+            # The oracle runs on the KV blocks these lists name (compact copies, ids remapped), so
+            # its gradient tensors have the size of what was touched, not of the whole head.
+            needed = index[0][valid].unique().long()
+            local = torch.searchsorted(needed, index[0].long().clamp_max(int(needed[-1]))).to(torch.int32)[None]
+            kv_rows = (needed[:, None] * BLOCK + offsets[None, :]).reshape(-1)
+            k_sub, v_sub = (x[kv_rows].clone().requires_grad_() for x in self.slots[1:])
             rows = (picked[:, None] * BLOCK + offsets[None, :]).reshape(-1)
             q_sub = self.slots[0][rows].clone().requires_grad_()
-            out, _ = oracle.fine_attention(q_sub, k_all, v_all, index, counts, layout.block_sizes, DIM ** -0.5)
-            torch.autograd.grad(out, (q_sub, k_all, v_all), self.dy[rows])
-            valid = torch.arange(index.shape[-1]) < counts[0][..., None]
+            out, _ = oracle.fine_attention(q_sub, k_sub, v_sub, local, counts, layout.block_sizes[needed],
+                                           DIM ** -0.5)
+            torch.autograd.grad(out, (q_sub, k_sub, v_sub), self.dy[rows])
             pairs += float(((sizes[index[0].long()] * valid).sum(-1) * sizes[picked][None, :]).sum())
             done_blocks += len(picked)
         return 3 * 4 * DIM * pairs, time.perf_counter() - start, done_blocks
