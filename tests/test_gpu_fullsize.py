@@ -117,3 +117,20 @@ def test_block_order_stack_h24_eight_layers_one_layout():
     dy = raster_to_block_wo_padding(_inputs(tokens, heads, 1, seed=1)[0], vsa_layout=layout)
     q, k, v, gate = (t.detach() for t in last)
     _check_call(layout, q, k, v, gate, dy, [0, 23], "block_order_stack_h24 layer 8")
+
+
+def test_ring_configuration_geometry_on_one_device_h24():
+    """The ring benchmark's geometry (video 61x90x160 at 0.95 + 4096 text tokens, 882,496 tokens,
+    801 listed blocks per query block, 14,720-block routing region) run whole on one device at 24
+    heads, one head value-checked against the FP32 oracle over every row.  Needs about 100 GB."""
+    if torch.cuda.get_device_properties(0).total_memory < 150 * 2 ** 30:
+        pytest.skip("needs a 180 GB device")
+    heads = 24
+    layout = build_vsa_layout(GEOMETRIES["c5"], head_num=heads, device="cuda", input_order="block")
+    q, k, v, gate = _inputs(layout.tokens, heads, 4)
+    dy = _inputs(layout.tokens, heads, 1, seed=1)[0]
+    _, _, index = _check_call(layout, q, k, v, gate, dy, [7], "ring_61x90x160_h24 on one device")
+    counts = layout.routing_counts
+    assert int(counts.min()) == int(counts.max()) == 801
+    assert (index[0][..., 1:] > index[0][..., :-1]).all(), "ascending, duplicate-free lists"
+    torch.cuda.empty_cache()
