@@ -90,9 +90,61 @@ VSA_DEVICE void named_barrier(int id, int threads) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
 }
 
+// Named barrier that also tells every thread whether `pred` held on all of them.
+VSA_DEVICE bool named_barrier_all(int id, int threads, bool pred) {
+  uint32_t all;
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\t"
+      "setp.ne.u32 q, %3, 0;\n\t"
+      "bar.red.and.pred p, %1, %2, q;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(all)
+      : "r"(id), "r"(threads), "r"(static_cast<uint32_t>(pred))
+      : "memory");
+  return all != 0;
+}
+
 VSA_DEVICE void fence_barrier_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
 // Make generic-proxy shared-memory writes visible to the async proxy (TMA, tcgen05.mma).
 VSA_DEVICE void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+// ------------------------------------------------------------------------------------------
+// Tile queue of a persistent kernel.  One scheduler thread takes tile numbers (block index first,
+// then an atomic counter), looks up what the roles need to know about the tile and publishes it
+// in a small ring in shared memory; every other role takes the entries in order.  `count < 0`
+// ends the sequence.  Entry `seq` lives in slot seq % kTileRing; its `full` barrier completes
+// once per publication, its `free` barrier once all `consumers` have arrived after reading.
+constexpr int kTileRing = 4;
+struct TileInfo {
+  int head, block, count, tile;
+};
+struct TileQueue {
+  TileInfo info[kTileRing];
+  uint64_t full[kTileRing], free_[kTileRing];
+};
+VSA_DEVICE void tile_queue_init(TileQueue& q, int consumers) {
+  for (int i = 0; i < kTileRing; ++i) {
+    mbar_init(&q.full[i], 1);
+    mbar_init(&q.free_[i], consumers);
+  }
+}
+// Scheduler thread: publish entry `seq`.
+VSA_DEVICE void tile_publish(TileQueue& q, int seq, const TileInfo& info, volatile int* abort_flag, int* status,
+                             int site) {
+  const int slot = seq % kTileRing, round = seq / kTileRing;
+  if (round >= 1) mbar_wait(&q.free_[slot], (round - 1) & 1, abort_flag, status, site);
+  q.info[slot] = info;
+  mbar_arrive(&q.full[slot]);
+}
+// Any other thread: read entry `seq`.  False when the sequence has ended or a wait gave up.
+VSA_DEVICE bool tile_take(TileQueue& q, int seq, TileInfo& info, volatile int* abort_flag, int* status, int site) {
+  const int slot = seq % kTileRing;
+  const bool ok = mbar_wait(&q.full[slot], (seq / kTileRing) & 1, abort_flag, status, site);
+  info = q.info[slot];
+  return ok && info.count >= 0;
+}
+// One arrival per consumer (a warp syncs first, then one lane arrives).
+VSA_DEVICE void tile_release(TileQueue& q, int seq) { mbar_arrive(&q.free_[seq % kTileRing]); }
 
 // ------------------------------------------------------------------------------------------
 // TMA: the tensor map views a [rows, heads, 128] BF16 tensor as (64 elements, rows, heads, 2 dim

@@ -7,6 +7,10 @@
 
 namespace vsa {
 
+// Zeroed work counter for one persistent kernel launch on `stream` (static device memory of the
+// current device; nothing is allocated).
+cudaError_t acquire_tile_counter(cudaStream_t stream, unsigned** counter);
+
 // ---------------------------------------------------------------------------- fine attention
 struct FineFwdParams {
   CUtensorMap q_map, k_map, v_map;  // [slots, heads, 128] BF16, box 64 x 1 x 64, 128-byte swizzle
@@ -35,6 +39,7 @@ struct FineFwdParams {
   int q_blocks, heads;
   float scale;
   int* status;
+  unsigned* tile_counter;           // set by the launcher
 };
 cudaError_t launch_fine_fwd(const FineFwdParams& params, bool merge, cudaStream_t stream);
 
