@@ -32,6 +32,8 @@ SIGNATURES = {
     "vsa_fine_fwd_strided": (_I32, [_P, _P, _P, _I64, _I64, _I32, _P, _P, _I64, _I64, _I32, _P, _F, _P, _P, _P, _P,
                                     _P, _I64, _I64, _P, _P, _I64, _P, _P]),
     "vsa_fine_fwd_running": (_I32, [_P, _P, _P, _I64, _I64, _I32, _P, _P, _I64, _I64, _I32, _P, _F, _P, _P, _P, _P]),
+    "vsa_fine_fwd_running_range": (_I32, [_P, _P, _P, _I64, _I64, _I32, _P, _P, _I64, _I64, _I32, _I32, _P, _F, _P,
+                                          _P, _P, _P]),
     "vsa_merge_bwd": (_I32, [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I64, _I64, _I32, _P]),
     "vsa_merge_bwd_strided": (_I32, [_P, _P, _I64, _I64, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I64, _I64, _I32, _P]),
     "vsa_kv_mask_words": (_I64, [_I64]),
@@ -41,6 +43,9 @@ SIGNATURES = {
     "vsa_fine_bwd_strided": (_I32, [_P, _P, _P, _P, _I64, _I64, _I32, _P, _P, _I64, _I64, _I32, _P, _P, _F, _P, _P,
                                     _P, _P, _P, _P, _I64, _I64, _I64, _I64, _P, _P, _P, _P, _P, _I32, _P, _P, _I32,
                                     _P, _P]),
+    "vsa_fine_bwd_range": (_I32, [_P, _P, _P, _P, _I64, _I64, _I32, _P, _P, _P, _I64, _I64, _I32, _I32, _P, _P, _F,
+                                  _P, _P, _P, _I32, _I32, _P, _P, _P, _I32, _I32, _P, _P]),
+    "vsa_list_bounds": (_I32, [_P, _P, _I64, _I32, _I32, _I32, _P, _P]),
     "vsa_partition_indices": (_I32, [_P, _P, _P, _P, _P, _I64, _I32, _I32, _I32, _I32, _I64, _I64, _P]),
     "vsa_merge_partial": (_I32, [_P, _P, _P, _P, _I64, _I32, _P]),
     "vsa_gate_merge": (_I32, [_P, _P, _P, _P, _P, _P, _P, _I64, _I32, _I64, _P]),

@@ -168,11 +168,14 @@ int fine_fwd_common(const void* q, const void* k, const void* v, int64_t q_block
                     int64_t count_head_stride, int32_t capacity, const int32_t* kv_sizes, float scale, void* o_slots,
                     float* lse, float* o_running, const int64_t* slot_row, const int32_t* block_coarse,
                     const void* gate, int64_t gate_row_stride, int64_t gate_head_stride, const void* coarse,
-                    void* out, int64_t out_rows, int32_t* status, void* stream) {
+                    void* out, int64_t out_rows, int32_t* status, void* stream,
+                    const int32_t* list_bounds = nullptr, int32_t bounds_stride = 0) {
   if (gate != nullptr && (bad_strides(gate_row_stride, gate_head_stride, heads) ||
                           (reinterpret_cast<uintptr_t>(gate) & 15) != 0))
     return vsa::kBadArgument;
-  if (q == nullptr || k == nullptr || v == nullptr || indices == nullptr || counts == nullptr ||
+  if (list_bounds != nullptr && bounds_stride < 2) return vsa::kBadArgument;
+  if (q == nullptr || k == nullptr || v == nullptr || indices == nullptr ||
+      (counts == nullptr && list_bounds == nullptr) ||
       (o_slots == nullptr && o_running == nullptr) || lse == nullptr || q_blocks < 0 || kv_blocks <= 0 ||
       heads <= 0 || capacity <= 0)
     return vsa::kBadArgument;
@@ -192,6 +195,8 @@ int fine_fwd_common(const void* q, const void* k, const void* v, int64_t q_block
   p.index_head_stride = index_head_stride;
   p.count_head_stride = count_head_stride;
   p.capacity = capacity;
+  p.list_bounds = list_bounds;
+  p.bounds_stride = bounds_stride;
   p.kv_sizes = kv_sizes;
   p.o_slots = static_cast<__nv_bfloat16*>(o_slots);
   p.lse = lse;
@@ -247,6 +252,17 @@ int vsa_fine_fwd_running(const void* q, const void* k, const void* v, int64_t q_
   return fine_fwd_common(q, k, v, q_blocks, kv_blocks, heads, indices, counts, index_head_stride, count_head_stride,
                          capacity, kv_sizes, scale, nullptr, lse_running, o_running, nullptr, nullptr, nullptr, 0, 0,
                          nullptr, nullptr, 0, status, stream);
+}
+
+int vsa_fine_fwd_running_range(const void* q, const void* k, const void* v, int64_t q_blocks, int64_t kv_blocks,
+                               int32_t heads, const int32_t* indices, const int32_t* list_bounds,
+                               int64_t index_head_stride, int64_t count_head_stride, int32_t bounds_stride,
+                               int32_t capacity, const int32_t* kv_sizes, float scale, float* o_running,
+                               float* lse_running, int32_t* status, void* stream) {
+  if (o_running == nullptr || list_bounds == nullptr) return vsa::kBadArgument;
+  return fine_fwd_common(q, k, v, q_blocks, kv_blocks, heads, indices, nullptr, index_head_stride, count_head_stride,
+                         capacity, kv_sizes, scale, nullptr, lse_running, o_running, nullptr, nullptr, nullptr, 0, 0,
+                         nullptr, nullptr, 0, status, stream, list_bounds, bounds_stride);
 }
 
 }  // extern "C" (reopened below)
@@ -316,8 +332,11 @@ int fine_bwd_common(const void* q, const void* k, const void* v, const void* d_o
                     const int64_t* q_slot_row, const int64_t* kv_slot_row, const void* dq_pool, const void* dk_pool,
                     const void* dv_pool, int32_t pool_f32, const int32_t* q_block_coarse,
                     const int32_t* kv_block_coarse, float* dq_f32, float* dk_f32, float* dv_f32,
-                    int32_t f32_accumulate, int32_t parts, int32_t* status, void* stream) {
+                    int32_t f32_accumulate, int32_t parts, int32_t* status, void* stream,
+                    const int32_t* list_bounds = nullptr, int32_t bounds_stride = 0, int32_t mask_word_begin = 0,
+                    int32_t mask_word_end = -1) {
   if (out_row_stride < static_cast<int64_t>(heads) * vsa::kDim || out_head_stride < vsa::kDim) return vsa::kBadArgument;
+  if (list_bounds != nullptr && bounds_stride < 2) return vsa::kBadArgument;
   if (q == nullptr || k == nullptr || v == nullptr || d_o == nullptr || indices == nullptr || counts == nullptr ||
       lse == nullptr || delta == nullptr || kv_mask == nullptr || q_blocks <= 0 || kv_blocks <= 0 || heads <= 0 ||
       capacity <= 0)
@@ -327,8 +346,11 @@ int fine_bwd_common(const void* q, const void* k, const void* v, const void* d_o
     return vsa::kBadArgument;
   if (q_blocks > 0x7fffffffLL / vsa::kBlock || kv_blocks > 0x7fffffffLL / vsa::kBlock || heads > 65535)
     return vsa::kTooLarge;
-  // The LSE / delta rows are fetched with 16-byte bulk copies.
-  if (((reinterpret_cast<uintptr_t>(lse) | reinterpret_cast<uintptr_t>(delta)) & 15) != 0) return vsa::kBadArgument;
+  // The LSE / delta rows are fetched with 16-byte bulk copies; the gradients are written with 16-byte stores.
+  if (((reinterpret_cast<uintptr_t>(lse) | reinterpret_cast<uintptr_t>(delta) | reinterpret_cast<uintptr_t>(dq) |
+        reinterpret_cast<uintptr_t>(dk) | reinterpret_cast<uintptr_t>(dv) | reinterpret_cast<uintptr_t>(dq_f32) |
+        reinterpret_cast<uintptr_t>(dk_f32) | reinterpret_cast<uintptr_t>(dv_f32)) & 15) != 0)
+    return vsa::kBadArgument;
   vsa::FineBwdParams p{};
   int rc = make_tile_map(&p.q_map, q, q_blocks * vsa::kBlock, heads);
   if (rc == vsa::kOk) rc = make_tile_map(&p.k_map, k, kv_blocks * vsa::kBlock, heads);
@@ -349,6 +371,12 @@ int fine_bwd_common(const void* q, const void* k, const void* v, const void* d_o
   p.delta = delta;
   p.kv_mask = kv_mask;
   p.mask_words = static_cast<int>(vsa_kv_mask_words(q_blocks));
+  p.list_bounds = list_bounds;
+  p.bounds_stride = bounds_stride;
+  p.mask_word_begin = mask_word_begin;
+  p.mask_word_end = mask_word_end < 0 ? p.mask_words : mask_word_end;
+  if (p.mask_word_begin < 0 || p.mask_word_end > p.mask_words || p.mask_word_begin > p.mask_word_end)
+    return vsa::kBadArgument;
   p.dq = static_cast<__nv_bfloat16*>(dq);
   p.dk = static_cast<__nv_bfloat16*>(dk);
   p.dv = static_cast<__nv_bfloat16*>(dv);
@@ -421,6 +449,30 @@ int vsa_fine_bwd_strided(const void* q, const void* k, const void* v, const void
                          out_row_stride, out_head_stride, q_out_rows, kv_out_rows, q_slot_row, kv_slot_row, dq_pool,
                          dk_pool, dv_pool, pool_f32, q_block_coarse, kv_block_coarse, nullptr, nullptr, nullptr, 0,
                          parts, status, stream);
+}
+
+int vsa_fine_bwd_range(const void* q, const void* k, const void* v, const void* d_o, int64_t q_blocks,
+                       int64_t kv_blocks, int32_t heads, const int32_t* indices, const int32_t* counts,
+                       const int32_t* list_bounds, int64_t index_head_stride, int64_t count_head_stride,
+                       int32_t bounds_stride, int32_t capacity, const int32_t* q_sizes, const int32_t* kv_sizes,
+                       float scale, const float* lse, const float* delta, uint32_t* kv_mask, int32_t mask_word_begin,
+                       int32_t mask_word_end, float* dq_f32, float* dk_f32, float* dv_f32, int32_t f32_accumulate,
+                       int32_t parts, int32_t* status, void* stream) {
+  if (mask_word_end < 0) return vsa::kBadArgument;
+  return fine_bwd_common(q, k, v, d_o, q_blocks, kv_blocks, heads, indices, counts, index_head_stride,
+                         count_head_stride, capacity, q_sizes, kv_sizes, scale, lse, delta, kv_mask, nullptr, nullptr,
+                         nullptr, static_cast<int64_t>(heads) * vsa::kDim, vsa::kDim, 0, 0, nullptr, nullptr, nullptr,
+                         nullptr, nullptr, 0, nullptr, nullptr, dq_f32, dk_f32, dv_f32, f32_accumulate, parts, status,
+                         stream, list_bounds, bounds_stride, mask_word_begin, mask_word_end);
+}
+
+int vsa_list_bounds(const int32_t* lists, const int32_t* counts, int64_t rows, int32_t capacity, int32_t chunk_blocks,
+                    int32_t chunks, int32_t* bounds, void* stream) {
+  if (lists == nullptr || counts == nullptr || bounds == nullptr || rows < 0 || capacity <= 0 || chunk_blocks <= 0 ||
+      chunks <= 0)
+    return vsa::kBadArgument;
+  return from_cuda(vsa::launch_list_bounds(lists, counts, rows, capacity, chunk_blocks, chunks, bounds,
+                                           as_stream(stream)));
 }
 
 int vsa_partition_indices(const int32_t* index, const int32_t* counts, const int64_t* global_to_gather,

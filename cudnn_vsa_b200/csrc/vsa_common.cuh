@@ -108,6 +108,20 @@ VSA_DEVICE void fence_barrier_init() { asm volatile("fence.mbarrier_init.release
 // Make generic-proxy shared-memory writes visible to the async proxy (TMA, tcgen05.mma).
 VSA_DEVICE void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
+// Position in a ring of three stages / buffers that keeps counting across tiles: `stage` of the
+// next pair, `phase` = parity of that stage's current fill, `round` = fills of stage 0 so far.
+struct Ring3 {
+  int stage = 0, round = 0;
+  uint32_t phase = 0;
+  VSA_DEVICE void advance() {
+    if (++stage == 3) {
+      stage = 0;
+      phase ^= 1;
+      ++round;
+    }
+  }
+};
+
 // ------------------------------------------------------------------------------------------
 // Tile queue of a persistent kernel.  One scheduler thread takes tile numbers (block index first,
 // then an atomic counter), looks up what the roles need to know about the tile and publishes it
@@ -115,8 +129,10 @@ VSA_DEVICE void fence_proxy_async_smem() { asm volatile("fence.proxy.async.share
 // ends the sequence.  Entry `seq` lives in slot seq % kTileRing; its `full` barrier completes
 // once per publication, its `free` barrier once all `consumers` have arrived after reading.
 constexpr int kTileRing = 4;
-struct TileInfo {
-  int head, block, count, tile;
+struct alignas(16) TileInfo {
+  int head, block, count;
+  int aux, aux2, aux3;  // kernel-specific (offset into the list, valid rows of the block, its coarse row, ...)
+  int reserved[2];
 };
 struct TileQueue {
   TileInfo info[kTileRing];

@@ -21,18 +21,20 @@ namespace vsa {
 
 namespace {
 
-// Epilogue of a transposed accumulator: this thread owns head dim `col % 128`, its columns are the
-// slots of `block`, of which the first `valid` are real and the first `computed` (a multiple of 16)
-// were produced by the products.  Adds `term` and writes BF16 to the mapped rows of `out`, or FP32
-// in slot order (added to the buffer's content when `accumulate`); padding slots are left alone.
-// BF16 element (row, this thread's head and dim) sits at row * out_row_stride + out_col.
-// A warp store covers 32 consecutive elements of one row.  The FP32 read-modify-write fetches a
-// whole chunk of old values before it stores any, so the loads are in flight together instead
-// of each waiting behind the previous store.
-VSA_DEVICE void store_grad_columns(bool have_acc, uint32_t tmem_addr, float term, const long long* out_rows,
-                                   long long out_limit, __nv_bfloat16* out, long long out_row_stride,
-                                   long long out_col, float* out_f32, bool accumulate, long long block,
-                                   long long width, long long col, int valid, int computed) {
+// Epilogue of a transposed accumulator, run by the 128 threads of one warpgroup (`t` = 0..127 =
+// TMEM lane = head dim): the columns are the slots of `block`, of which the first `valid` are real
+// and the first `computed` (a multiple of 16) were produced by the products.  The tile is turned
+// through `turn` (shared memory, 16 KiB for BF16 output, 32 KiB for FP32) so that global memory
+// sees 16-byte accesses of whole row segments: `term` is added, then BF16 rows go to the mapped
+// rows of `out` (row r, this head at out + row * out_row_stride + head_offset), or FP32 rows in
+// slot order to `out_f32` (added to the buffer's content when `accumulate`).  Padding slots are
+// left alone.  The FP32 read-modify-write fetches a batch of old values before it stores any, so
+// the loads are in flight together.
+VSA_DEVICE void store_grad_tile(bool have_acc, uint32_t tmem_addr, float term, uint8_t* turn, int barrier_id, int t,
+                                const long long* out_rows, long long out_limit, __nv_bfloat16* out,
+                                long long out_row_stride, long long head_offset, float* out_f32, bool accumulate,
+                                long long block, long long width, long long head_col, int valid, int computed) {
+  const bool f32_out = out_f32 != nullptr;
 #pragma unroll
   for (int c = 0; c < 2; ++c) {
     if (c * 32 >= valid) break;
@@ -41,22 +43,47 @@ VSA_DEVICE void store_grad_columns(bool have_acc, uint32_t tmem_addr, float term
       VSA_TMEM_LD_32x32b_X32(bits, tmem_addr + c * 32);
       tmem_wait_ld();
     }
-    if (out_f32 != nullptr) {
-      float* base = out_f32 + (block * kBlock + c * 32) * width + col;
-      float old[32];
+    if (f32_out) {
+      float* at = reinterpret_cast<float*>(turn) + c * 32 * kDim + t;
 #pragma unroll
-      for (int i = 0; i < 32; ++i) old[i] = (accumulate && c * 32 + i < valid) ? base[i * width] : 0.f;
-#pragma unroll
-      for (int i = 0; i < 32; ++i)
-        if (c * 32 + i < valid) base[i * width] = old[i] + (__uint_as_float(bits[i]) + term);
+      for (int i = 0; i < 32; ++i) at[i * kDim] = __uint_as_float(bits[i]) + term;
     } else {
+      __nv_bfloat16* at = reinterpret_cast<__nv_bfloat16*>(turn) + c * 32 * kDim + t;
 #pragma unroll
-      for (int i = 0; i < 32; ++i) {
-        const int r = c * 32 + i;
-        const long long row = out_rows[r];
-        if (r < valid && row >= 0 && row < out_limit)
-          out[row * out_row_stride + out_col] = __float2bfloat16(__uint_as_float(bits[i]) + term);
+      for (int i = 0; i < 32; ++i) at[i * kDim] = __float2bfloat16(__uint_as_float(bits[i]) + term);
+    }
+  }
+  named_barrier(barrier_id, 128);
+  if (f32_out) {
+    const float4* rows = reinterpret_cast<const float4*>(turn);  // 32 vectors per row
+    float4* base = reinterpret_cast<float4*>(out_f32 + block * kBlock * width + head_col);
+    const long long row_vecs = width / 4;
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      if (half * 32 >= valid) break;
+      float4 old[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const int v = t + (half * 8 + j) * 128, r = v >> 5, c = v & 31;
+        old[j] = (accumulate && r < valid) ? base[r * row_vecs + c] : make_float4(0.f, 0.f, 0.f, 0.f);
       }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const int v = t + (half * 8 + j) * 128, r = v >> 5, c = v & 31;
+        if (r < valid) {
+          const float4 x = rows[v];
+          base[r * row_vecs + c] = make_float4(old[j].x + x.x, old[j].y + x.y, old[j].z + x.z, old[j].w + x.w);
+        }
+      }
+    }
+  } else {
+    const uint4* rows = reinterpret_cast<const uint4*>(turn);  // 16 vectors per row
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int v = t + j * 128, r = v >> 4, c = v & 15;
+      if (r >= valid) break;
+      const long long row = out_rows[r];
+      if (row >= 0 && row < out_limit) *reinterpret_cast<uint4*>(out + row * out_row_stride + head_offset + c * 8) = rows[v];
     }
   }
 }
@@ -89,13 +116,13 @@ struct DkvSmem {  // placed at a 1024-byte aligned address; every tile offset is
 // Every thread that needs the sequence keeps its own cursor, so nothing is passed through
 // shared memory.
 struct MaskCursor {
-  const uint32_t* words;
-  int count, word;
+  const uint32_t* words;  // the whole row
+  int end, word;          // walks words [first, end)
   uint32_t bits;
-  VSA_DEVICE MaskCursor(const uint32_t* w, int c) : words(w), count(c), word(0), bits(c > 0 ? w[0] : 0u) {}
+  VSA_DEVICE MaskCursor(const uint32_t* w, int first, int e) : words(w), end(e), word(first), bits(first < e ? w[first] : 0u) {}
   VSA_DEVICE int next() {
     while (bits == 0) {
-      if (++word >= count) return 0;
+      if (++word >= end) return 0;
       bits = words[word];
     }
     const int bit = __ffs(bits) - 1;
@@ -183,7 +210,7 @@ __global__ void __launch_bounds__(kDkvThreads, 1) fine_bwd_dkv_kernel(const __gr
   const int qrow = tid & 127;         // query row of the pair owned by this thread (math role) / head dim (epilogue)
   const uint32_t* mask = p.kv_mask + (static_cast<long long>(head) * p.kv_blocks + kvb) * p.mask_words;
   int n = 0;
-  for (int w = 0; w < p.mask_words; ++w) n += __popc(mask[w]);
+  for (int w = p.mask_word_begin; w < p.mask_word_end; ++w) n += __popc(mask[w]);
 
   if (tid == 0) {
     mbar_init(&sm.kv_full, 1);
@@ -219,7 +246,7 @@ __global__ void __launch_bounds__(kDkvThreads, 1) fine_bwd_dkv_kernel(const __gr
   const uint32_t tmem = sm.tmem_base;
   const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
   volatile int* abort_flag = &sm.abort_flag;
-  MaskCursor cursor(mask, p.mask_words);
+  MaskCursor cursor(mask, p.mask_word_begin, p.mask_word_end);
   const int kv_size = p.kv_sizes != nullptr ? p.kv_sizes[kvb] : kBlock;
   // Keys the products cover: the block's valid keys rounded up to the MMA's N granularity.  A
   // short block (an edge tile of 8, 12, 16 ... keys) runs every product with a narrow N, moves a
@@ -383,18 +410,24 @@ __global__ void __launch_bounds__(kDkvThreads, 1) fine_bwd_dkv_kernel(const __gr
       mbar_wait(&sm.dkv_final, 0, abort_flag, p.status, 27);
       tc_fence_after();
     }
-    // Thread = head dim `qrow`; warpgroup 0 writes dK, warpgroup 1 writes dV.
+    // Thread = head dim `qrow`; warpgroup 0 writes dK, warpgroup 1 writes dV, each turning its tile
+    // through its own half of the P / dS buffers (idle: every gradient product has completed).
     const long long width = static_cast<long long>(p.heads) * kDim;
     const long long col = static_cast<long long>(head) * kDim + qrow;
-    const long long out_col = static_cast<long long>(head) * p.out_head_stride + qrow;
-    if (group == 0) {
+    const long long head_col = static_cast<long long>(head) * kDim;
+    const long long head_offset = static_cast<long long>(head) * p.out_head_stride;
+    // A tile without listed query blocks adds nothing to a running FP32 sum.
+    const bool nothing = n == 0 && p.f32_accumulate != 0 && p.dk_f32 != nullptr && p.dk_pool == nullptr &&
+                         p.dv_pool == nullptr;
+    if (nothing) {
+    } else if (group == 0) {
       const float term = pool_term(p.dk_pool, p.pool_f32, p.kv_block_coarse, kvb, kv_size, width, col);
-      store_grad_columns(n > 0, tmem + lane_base + kColDk, term, sm.out_row, p.kv_out_rows, p.dk, p.out_row_stride,
-                         out_col, p.dk_f32, p.f32_accumulate != 0, kvb, width, col, kv_size, kv_n);
+      store_grad_tile(n > 0, tmem + lane_base + kColDk, term, sm.pt[0], 2, qrow, sm.out_row, p.kv_out_rows, p.dk,
+                      p.out_row_stride, head_offset, p.dk_f32, p.f32_accumulate != 0, kvb, width, head_col, kv_size, kv_n);
     } else {
       const float term = pool_term(p.dv_pool, p.pool_f32, p.kv_block_coarse, kvb, kv_size, width, col);
-      store_grad_columns(n > 0, tmem + lane_base + kColDv, term, sm.out_row, p.kv_out_rows, p.dv, p.out_row_stride,
-                         out_col, p.dv_f32, p.f32_accumulate != 0, kvb, width, col, kv_size, kv_n);
+      store_grad_tile(n > 0, tmem + lane_base + kColDv, term, sm.dst[0], 3, qrow, sm.out_row, p.kv_out_rows, p.dv,
+                      p.out_row_stride, head_offset, p.dv_f32, p.f32_accumulate != 0, kvb, width, head_col, kv_size, kv_n);
     }
   }
   tc_fence_before();

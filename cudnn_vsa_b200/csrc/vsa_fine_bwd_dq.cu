@@ -1,7 +1,12 @@
 // Block-sparse fine attention, backward, dQ kernel for sm_100a.
 //
-// One CTA owns one (query block, head) and walks the block's KV list two blocks ("a pair") at a
-// time.  Every product puts 128 rows on the tensor core's M axis, the shape it runs at full rate:
+// A tile is one (query block, head): the CTA walks the block's KV list two blocks ("a pair") at a
+// time.  The kernel is persistent - one CTA per SM takes tiles in head-major order from a work
+// counter; the thread that loads Q, dO and K publishes each tile's head, block, list length and
+// valid rows in a small shared-memory queue that the other roles read in order - so barriers,
+// tensor memory and the stage rings are set up once, the loads of the next tile run under the
+// last pairs and the epilogue of the current one, and the per-row data of the next tile (LSE,
+// delta, output rows) is fetched while the epilogue stores.  Every product puts 128 rows on the tensor core's M axis, the shape it runs at full rate:
 //   S^T  = K Q^T        M = 128 keys of the pair,  N = 64 queries,  K = 128 head dims
 //   dP^T = V dO^T       M = 128 keys,              N = 64 queries,  K = 128 head dims
 //   dQ^T += K^T dS^T    M = 128 head dims,         N = 64 queries,  K = 128 keys
@@ -43,9 +48,10 @@ struct DqSmem {  // placed at a 1024-byte aligned address; every tile offset is 
   uint8_t ds[2][kTileBytes];  // per warpgroup: dS^T [128 keys][64 queries] BF16, 128-byte swizzle
   float neg_lse2[kBlock];     // -lse * log2(e) per query row (-inf for a row without keys)
   float delta[kBlock];
-  long long out_row[kBlock];
-  uint64_t qdo_full, k_full[kKStages], v_full[kVStages], k_free[kKStages], v_free[kVStages];
-  uint64_t sp_done[2], sp_free[2], ds_ready[2], ds_free[2], dq_final;
+  long long out_row[2][kBlock];  // by tile parity: the next tile's rows are staged while this tile's are stored
+  uint64_t qdo_full, qdo_free, k_full[kKStages], v_full[kVStages], k_free[kKStages], v_free[kVStages];
+  uint64_t sp_done[2], sp_free[2], ds_ready[2], ds_free[2], dq_final, dq_free;
+  TileQueue tiles;
   uint32_t tmem_base;
   int abort_flag;
 };
@@ -116,18 +122,23 @@ __global__ void __launch_bounds__(kThreads, 1) fine_bwd_dq_kernel(const __grid_c
   extern __shared__ uint8_t smem_raw[];
   DqSmem& sm = *reinterpret_cast<DqSmem*>(smem_raw + ((1024 - (smem_u32(smem_raw) & 1023)) & 1023));
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int qb = blockIdx.x, head = blockIdx.y;
   const int group = (warp >> 2) & 1;  // score-math warpgroup (warps 0..7 only)
   const int key = tid & 127;          // key of the pair owned by this thread (math role) / head dim (epilogue)
-  const int n = p.counts[static_cast<long long>(head) * p.count_head_stride + qb];
-  const int32_t* list = p.indices + static_cast<long long>(head) * p.index_head_stride +
-                        static_cast<long long>(qb) * p.capacity;
+  const int tiles = p.q_blocks * p.heads;  // tile t = (head, query block), head-major
+  // Consumers of the tile queue: the V producer, the two issuing warps, the eight math warps.
+  constexpr int kQueueConsumers = 11;
   // Query rows the products cover: the block's valid rows rounded up to the MMA's N granularity.
-  const int q_size = p.q_sizes != nullptr ? p.q_sizes[qb] : kBlock;
-  const int q_n = q_size >= kBlock ? kBlock : (q_size <= 16 ? 16 : ((q_size + 15) & ~15));
+  auto covered_rows = [](int q_size) -> int {
+    return q_size >= kBlock ? kBlock : (q_size <= 16 ? 16 : ((q_size + 15) & ~15));
+  };
+  auto list_of = [&](const TileInfo& t) -> const int32_t* {
+    return p.indices + static_cast<long long>(t.head) * p.index_head_stride + static_cast<long long>(t.block) * p.capacity +
+           t.aux3;
+  };
 
   if (tid == 0) {
     mbar_init(&sm.qdo_full, 1);
+    mbar_init(&sm.qdo_free, 1);
     for (int i = 0; i < kKStages; ++i) {
       mbar_init(&sm.k_full[i], 1);
       mbar_init(&sm.k_free[i], 1);
@@ -143,19 +154,14 @@ __global__ void __launch_bounds__(kThreads, 1) fine_bwd_dq_kernel(const __grid_c
       mbar_init(&sm.ds_free[i], 1);
     }
     mbar_init(&sm.dq_final, 1);
+    mbar_init(&sm.dq_free, kMathThreads);
+    tile_queue_init(sm.tiles, kQueueConsumers);
     sm.abort_flag = 0;
     fence_barrier_init();
     tma_prefetch_desc(&p.q_map);
     tma_prefetch_desc(&p.do_map);
     tma_prefetch_desc(&p.k_half_map);
     tma_prefetch_desc(&p.v_half_map);
-  }
-  if (tid < kBlock) {
-    const long long s = static_cast<long long>(qb) * kBlock + tid;
-    sm.out_row[tid] = p.q_slot_row != nullptr ? p.q_slot_row[s] : s;
-    const float lse = p.lse[static_cast<long long>(head) * p.q_slots + s];
-    sm.neg_lse2[tid] = lse == -INFINITY ? -INFINITY : -lse * kLog2eBwd;
-    sm.delta[tid] = p.delta[static_cast<long long>(head) * p.q_slots + s];
   }
   if (warp == 0) {
     tmem_alloc(&sm.tmem_base, kTmemCols);
@@ -167,89 +173,156 @@ __global__ void __launch_bounds__(kThreads, 1) fine_bwd_dq_kernel(const __grid_c
   const uint32_t tmem = sm.tmem_base;
   const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
   volatile int* abort_flag = &sm.abort_flag;
+  static_assert(kKStages == 3 && kVStages == 2, "the stage rings below are written for 3 K and 2 V stages");
 
   // Barrier discipline: a barrier is only ever waited on for its NEWEST commit or arrival round;
   // every barrier belongs to one buffer and the round after the awaited one cannot start before
-  // the waiter has moved on.
-  const int pairs = (n + 1) >> 1;
-  if (warp == 9 || warp == 10) {
-    // ------------------------------------------------------------ producers: TMA loads
+  // the waiter has moved on.  Pairs are numbered through all tiles of the CTA (`g` below): pair
+  // g uses accumulator set, dS^T buffer and math warpgroup g & 1, V stage g & 1 and K stage
+  // g % 3, whatever tile it belongs to; `used` counts the non-empty tiles so far.  Every role
+  // skips empty tiles.
+  if (warp == 9) {
+    // ------------------------------------------------------------ producer of Q, dO and K; scheduler
     // K and V have a producer warp each: V stages are released after dP^T, K stages only after
     // the dQ product, and one in-order loop would hold each load behind the other's wait.
-    if (lane == 0 && n > 0) {
-      const bool is_k = warp == 9;
-      if (is_k) {
+    if (lane == 0) {
+      Ring3 ring;
+      int used = 0;
+      // Tile numbers: the block index first, then the work counter.  The next number is taken
+      // only when the last loads of the current tile are about to be issued - a CTA that held
+      // tiles in reserve would keep them from idle SMs at the end of the launch, and one list
+      // can be a hundred times longer than another - which still leaves the counter and the
+      // tile's list length a few pairs of time to arrive.
+      auto info_of = [&](int t) -> TileInfo {
+        if (t >= tiles) return TileInfo{0, 0, -1};
+        const int head = t / p.q_blocks, qb = t - head * p.q_blocks;
+        // aux = valid rows of the query block, aux2 = row of its pooled-mean gradient (-1 = none),
+        // aux3 = first entry of the list's sub-range.
+        int pool_row = -1;
+        if (p.dq_pool != nullptr) pool_row = p.pool_f32 ? qb : (p.q_block_coarse != nullptr ? p.q_block_coarse[qb] : -1);
+        const int q_size = p.q_sizes != nullptr ? p.q_sizes[qb] : kBlock;
+        const long long row = static_cast<long long>(head) * p.count_head_stride + qb;
+        if (p.list_bounds == nullptr) return TileInfo{head, qb, p.counts[row], q_size, pool_row, 0};
+        const int32_t* bounds = p.list_bounds + row * p.bounds_stride;
+        const int begin = bounds[0];
+        return TileInfo{head, qb, bounds[1] - begin, q_size, pool_row, begin};
+      };
+      auto take_number = [&]() -> int { return static_cast<int>(gridDim.x + atomicAdd(p.tile_counter, 1u)); };
+      TileInfo cur = info_of(static_cast<int>(blockIdx.x));
+      for (int seq = 0;; ++seq) {
+        tile_publish(sm.tiles, seq, cur, abort_flag, p.status, 40);
+        if (cur.count < 0 || *abort_flag) break;  // end of the tiles, or a wait gave up: start no further loads
+        const TileInfo now = cur;
+        const int n = now.count;
+        if (n == 0) {
+          cur = info_of(take_number());
+          continue;
+        }
+        const int32_t* list = list_of(now);
+        const int pairs = (n + 1) >> 1;
+        // Q and dO have one buffer: it is free once the previous tile's last score products are done.
+        if (used >= 1) mbar_wait(&sm.qdo_free, (used - 1) & 1, abort_flag, p.status, 38);
         mbar_expect_tx(&sm.qdo_full, 2 * kTileBytes);
-        tma_load_tile(sm.q, &p.q_map, &sm.qdo_full, head, qb);
-        tma_load_tile(sm.d_o, &p.do_map, &sm.qdo_full, head, qb);
+        tma_load_tile(sm.q, &p.q_map, &sm.qdo_full, now.head, now.block);
+        tma_load_tile(sm.d_o, &p.do_map, &sm.qdo_full, now.head, now.block);
+        const int claim_at = pairs > kKStages ? pairs - kKStages : 0;
+        int t_next = tiles;
+        for (int i = 0; i < pairs; ++i) {
+          if (i == claim_at) t_next = take_number();
+          const int count = (2 * i + 1 < n) ? 2 : 1;
+          const int stage = ring.stage;
+          if (ring.round >= 1) mbar_wait(&sm.k_free[stage], ring.phase ^ 1, abort_flag, p.status, 12);
+          mbar_expect_tx(&sm.k_full[stage], count * kTileBytes);
+          for (int t = 0; t < count; ++t)
+            for (int h = 0; h < 2; ++h)
+              tma_load_half(sm.k[stage] + h * kTileBytes + t * kHalfTileBytes, &p.k_half_map, &sm.k_full[stage], now.head,
+                            list[2 * i + t], h);
+          ring.advance();
+        }
+        ++used;
+        cur = info_of(t_next);
       }
-      const CUtensorMap* map = is_k ? &p.k_half_map : &p.v_half_map;
-      const int stages = is_k ? kKStages : kVStages;
-      int stage = 0;
-      uint32_t round = 0;  // parity of the release awaited before refilling the stage
-      for (int i = 0; i < pairs; ++i) {
-        const int count = (2 * i + 1 < n) ? 2 : 1;
-        uint64_t* full = is_k ? &sm.k_full[stage] : &sm.v_full[stage];
-        uint8_t* dst = is_k ? sm.k[stage] : sm.v[stage];
-        if (i >= stages) mbar_wait(is_k ? &sm.k_free[stage] : &sm.v_free[stage], round, abort_flag, p.status, 12);
-        mbar_expect_tx(full, count * kTileBytes);
-        for (int t = 0; t < count; ++t)
-          for (int h = 0; h < 2; ++h) tma_load_half(dst + h * kTileBytes + t * kHalfTileBytes, map, full, head, list[2 * i + t], h);
-        if (++stage == stages) {
-          stage = 0;
-          if (i >= stages) round ^= 1;
+    }
+  } else if (warp == 10) {
+    // ------------------------------------------------------------ producer of V
+    if (lane == 0) {
+      int g = 0;
+      TileInfo info;
+      for (int seq = 0; tile_take(sm.tiles, seq, info, abort_flag, p.status, 41); ++seq) {
+        tile_release(sm.tiles, seq);
+        const int n = info.count;
+        if (n == 0) continue;
+        const int32_t* list = list_of(info);
+        const int pairs = (n + 1) >> 1;
+        for (int i = 0; i < pairs; ++i, ++g) {
+          const int count = (2 * i + 1 < n) ? 2 : 1;
+          const int stage = g & 1;
+          if (g >= 2) mbar_wait(&sm.v_free[stage], ((g >> 1) - 1) & 1, abort_flag, p.status, 20);
+          mbar_expect_tx(&sm.v_full[stage], count * kTileBytes);
+          for (int t = 0; t < count; ++t)
+            for (int h = 0; h < 2; ++h)
+              tma_load_half(sm.v[stage] + h * kTileBytes + t * kHalfTileBytes, &p.v_half_map, &sm.v_full[stage], info.head,
+                            list[2 * i + t], h);
         }
       }
     }
   } else if (warp == 11) {
     // ------------------------------------------------------------ issuer of the score products
     // Two issuing warps, one per kind of product, synchronised only through the barriers: the
-    // score products of pair j + 2 start as soon as their operands have landed and warpgroup
-    // j & 1 has pulled pair j out of the accumulators, whatever the dQ products are waiting for.
+    // score products of pair g + 2 start as soon as their operands have landed and warpgroup
+    // g & 1 has pulled pair g out of the accumulators, whatever the dQ products are waiting for.
     // The whole warp walks the loop (uniform control flow and addresses); one elected lane
     // issues the MMAs and commits.
-    if (n > 0) {
-      const bool leader = elect_one();
-      const uint32_t q_lo = umma_desc_lo(smem_u32(sm.q), 16);
-      const uint32_t do_lo = umma_desc_lo(smem_u32(sm.d_o), 16);
-      const uint32_t k_lo0 = umma_desc_lo(smem_u32(sm.k[0]), 16);
-      const uint32_t v_lo0 = umma_desc_lo(smem_u32(sm.v[0]), 16);
-      constexpr uint32_t kPairLo = kPairBytes >> 4;
-      int s_k = 0, s_v = 0;                   // stages of the next score products
-      uint32_t s_k_phase = 0, s_v_phase = 0;  // parities of those stages' current fills
-      const uint32_t idesc = umma_idesc(128, q_n, 0, 0);
-      mbar_wait(&sm.qdo_full, 0, abort_flag, p.status, 11);
-      for (int j = 0; j < pairs; ++j) {
-        if (j >= 2) mbar_wait(&sm.sp_free[j & 1], ((j >> 1) - 1) & 1, abort_flag, p.status, 17);
-        mbar_wait(&sm.k_full[s_k], s_k_phase, abort_flag, p.status, 15);
+    const bool leader = elect_one();
+    const uint32_t q_lo = umma_desc_lo(smem_u32(sm.q), 16);
+    const uint32_t do_lo = umma_desc_lo(smem_u32(sm.d_o), 16);
+    const uint32_t k_lo0 = umma_desc_lo(smem_u32(sm.k[0]), 16);
+    const uint32_t v_lo0 = umma_desc_lo(smem_u32(sm.v[0]), 16);
+    constexpr uint32_t kPairLo = kPairBytes >> 4;
+    Ring3 ring;  // K stage of the next score products
+    int g = 0, used = 0;
+    TileInfo info;
+    for (int seq = 0; __all_sync(0xffffffffu, tile_take(sm.tiles, seq, info, abort_flag, p.status, 42)); ++seq) {
+      if (leader) tile_release(sm.tiles, seq);  // after the vote, so every lane has read the entry
+      const int n = info.count;
+      if (n == 0) continue;
+      const int pairs = (n + 1) >> 1;
+      const uint32_t idesc = umma_idesc(128, covered_rows(info.aux), 0, 0);
+      mbar_wait(&sm.qdo_full, used & 1, abort_flag, p.status, 11);
+      for (int j = 0; j < pairs; ++j, ++g) {
+        const int set = g & 1;
+        if (g >= 2) mbar_wait(&sm.sp_free[set], ((g >> 1) - 1) & 1, abort_flag, p.status, 17);
+        mbar_wait(&sm.k_full[ring.stage], ring.phase, abort_flag, p.status, 15);
         tc_fence_after();
-        if (leader) issue_scores(tmem + (j & 1) * 128, k_lo0 + s_k * kPairLo, q_lo, idesc);
-        mbar_wait(&sm.v_full[s_v], s_v_phase, abort_flag, p.status, 19);
+        if (leader) issue_scores(tmem + set * 128, k_lo0 + ring.stage * kPairLo, q_lo, idesc);
+        mbar_wait(&sm.v_full[set], (g >> 1) & 1, abort_flag, p.status, 19);
         tc_fence_after();
         if (leader) {
-          issue_scores(tmem + (j & 1) * 128 + 64, v_lo0 + s_v * kPairLo, do_lo, idesc);
-          umma_commit(&sm.sp_done[j & 1]);
-          umma_commit(&sm.v_free[s_v]);
+          issue_scores(tmem + set * 128 + 64, v_lo0 + set * kPairLo, do_lo, idesc);
+          umma_commit(&sm.sp_done[set]);
+          umma_commit(&sm.v_free[set]);
+          if (j + 1 == pairs) umma_commit(&sm.qdo_free);  // Q and dO have been read for the last time
         }
-        if (++s_k == kKStages) {
-          s_k = 0;
-          s_k_phase ^= 1;
-        }
-        if (++s_v == kVStages) {
-          s_v = 0;
-          s_v_phase ^= 1;
-        }
+        ring.advance();
       }
+      ++used;
     }
   } else if (warp == 8) {
     // ------------------------------------------------------------ issuer of the dQ products
-    if (n > 0) {
-      const bool leader = elect_one();
-      const uint32_t k_mn_lo0 = umma_desc_lo(smem_u32(sm.k[0]), kTileBytes);
-      const uint32_t ds_lo0 = umma_desc_lo(smem_u32(sm.ds[0]), kHalfTileBytes);
-      constexpr uint32_t kPairLo = kPairBytes >> 4, kDsLo = kTileBytes >> 4;
-      int d_k = 0;  // K stage of the next dQ product
-      const uint32_t idesc = umma_idesc(128, q_n, 1, 1);
+    const bool leader = elect_one();
+    const uint32_t k_mn_lo0 = umma_desc_lo(smem_u32(sm.k[0]), kTileBytes);
+    const uint32_t ds_lo0 = umma_desc_lo(smem_u32(sm.ds[0]), kHalfTileBytes);
+    constexpr uint32_t kPairLo = kPairBytes >> 4, kDsLo = kTileBytes >> 4;
+    int d_k = 0;  // K stage of the next dQ product
+    int g = 0, used = 0;
+    TileInfo info;
+    for (int seq = 0; __all_sync(0xffffffffu, tile_take(sm.tiles, seq, info, abort_flag, p.status, 43)); ++seq) {
+      if (leader) tile_release(sm.tiles, seq);
+      const int n = info.count;
+      if (n == 0) continue;
+      const int pairs = (n + 1) >> 1;
+      const int32_t* list = list_of(info);
+      const uint32_t idesc = umma_idesc(128, covered_rows(info.aux), 1, 1);
       // K=16 steps that hold real keys, per block of the pair; looked up one pair ahead so the
       // two dependent loads never sit between a completed wait and its products.
       auto steps_of = [&](int i, int& s0, int& s1) {
@@ -263,111 +336,219 @@ __global__ void __launch_bounds__(kThreads, 1) fine_bwd_dq_kernel(const __grid_c
       };
       int steps0 = 4, steps1 = 0;
       steps_of(0, steps0, steps1);
-      for (int i = 0; i < pairs; ++i) {
+      // The first product of a tile overwrites dQ^T: the epilogue of the previous tile must have read it.
+      if (used >= 1) mbar_wait(&sm.dq_free, (used - 1) & 1, abort_flag, p.status, 39);
+      for (int i = 0; i < pairs; ++i, ++g) {
         const int now0 = steps0, now1 = steps1;
         if (i + 1 < pairs) steps_of(i + 1, steps0, steps1);
-        mbar_wait(&sm.ds_ready[i & 1], (i >> 1) & 1, abort_flag, p.status, 18);
+        const int set = g & 1;
+        mbar_wait(&sm.ds_ready[set], (g >> 1) & 1, abort_flag, p.status, 18);
         tc_fence_after();
         if (leader) {
-          issue_dq(tmem + kColDq, k_mn_lo0 + d_k * kPairLo, ds_lo0 + (i & 1) * kDsLo, now0, now1, i > 0, idesc);
+          issue_dq(tmem + kColDq, k_mn_lo0 + d_k * kPairLo, ds_lo0 + set * kDsLo, now0, now1, i > 0, idesc);
           umma_commit(&sm.k_free[d_k]);
-          umma_commit(&sm.ds_free[i & 1]);
+          umma_commit(&sm.ds_free[set]);
+          if (i + 1 == pairs) umma_commit(&sm.dq_final);
         }
         if (++d_k == kKStages) d_k = 0;
       }
-      if (leader) umma_commit(&sm.dq_final);
+      ++used;
     }
   } else {
-    // ------------------------------------------------------------ score math warpgroups
+    // ------------------------------------------------------------ score math warpgroups and epilogue
     const uint32_t tmem_s = tmem + lane_base + group * 128;
     uint8_t* ds_row = sm.ds[group] + key * 128;
     const int tile = key >> 6, key_in_block = key & 63;
     const float scale = p.scale, sl2 = p.scale * kLog2eBwd;
-    // The valid length of a block comes from two dependent global loads (list, then sizes).  They
-    // are software-pipelined over two rounds - the block id is fetched two rounds ahead, the size
-    // one round ahead from an id that is already in a register - so no load is issued behind the
-    // one it depends on.
-    int size_next = kBlock;
-    if (p.kv_sizes != nullptr && 2 * group + tile < n) size_next = p.kv_sizes[list[2 * group + tile]];
-    int block_next = (p.kv_sizes != nullptr && 2 * group + 4 + tile < n) ? list[2 * group + 4 + tile] : 0;
-    for (int i = group; i < pairs; i += 2) {
-      const bool live = (2 * i + tile < n) && key_in_block < size_next;
+    const long long width = static_cast<long long>(p.heads) * kDim;
+
+    // What a tile needs before its first pair is fetched while the previous tile's epilogue runs:
+    // LSE, delta and output row of query row `tid` (threads 0..63) into registers, staged into
+    // shared memory before the epilogue's first barrier, and the first steps of the block-size
+    // lookups below.  The valid length of a block comes from two dependent global loads (list,
+    // then sizes); they are software-pipelined over two rounds - the block id is fetched two
+    // rounds ahead, the size one round ahead from an id that is already in a register - so no
+    // load is issued behind the one it depends on.  Between tiles the ids are fetched before
+    // the epilogue and the first size after it.
+    float pre_lse = 0.f, pre_delta = 0.f;
+    long long pre_row = 0;
+    int size_next = kBlock, block_next = 0, block_first = -1;
+    auto fetch_rows_and_ids = [&](const TileInfo& t, int first_pair) {
+      if (tid < kBlock) {
+        const long long s = static_cast<long long>(t.block) * kBlock + tid;
+        pre_row = p.q_slot_row != nullptr ? p.q_slot_row[s] : s;
+        pre_lse = p.lse[static_cast<long long>(t.head) * p.q_slots + s];
+        pre_delta = p.delta[static_cast<long long>(t.head) * p.q_slots + s];
+      }
+      const int32_t* list = list_of(t);
+      block_first = -1;
+      block_next = 0;
       if (p.kv_sizes != nullptr) {
-        if (2 * i + 4 + tile < n) size_next = p.kv_sizes[block_next];
-        if (2 * i + 8 + tile < n) block_next = list[2 * i + 8 + tile];
+        if (2 * first_pair + tile < t.count) block_first = list[2 * first_pair + tile];
+        if (2 * first_pair + 4 + tile < t.count) block_next = list[2 * first_pair + 4 + tile];
       }
-      mbar_wait(&sm.sp_done[group], (i >> 1) & 1, abort_flag, p.status, 13);
-      tc_fence_after();
-      uint32_t packed[32];
-#pragma unroll
-      for (int c = 0; c < 2; ++c) {
-        if (c * 32 >= q_n) break;  // a short query block has no second half
-        uint32_t s_bits[32], dp_bits[32];
-        VSA_TMEM_LD_32x32b_X32(s_bits, tmem_s + c * 32);
-        VSA_TMEM_LD_32x32b_X32(dp_bits, tmem_s + 64 + c * 32);
-        tmem_wait_ld();
-        if ((c + 1) * 32 >= q_n) {
-          // All of S^T and dP^T is in registers: the accumulators may be overwritten.
-          tc_fence_before();
-          mbar_arrive(&sm.sp_free[group]);
+    };
+    auto stage_rows = [&](int parity) {
+      if (tid < kBlock) {
+        sm.out_row[parity][tid] = pre_row;
+        sm.neg_lse2[tid] = pre_lse == -INFINITY ? -INFINITY : -pre_lse * kLog2eBwd;
+        sm.delta[tid] = pre_delta;
+      }
+    };
+    auto fetch_first_size = [&]() { size_next = block_first >= 0 ? p.kv_sizes[block_first] : kBlock; };
+
+    int g0 = 0;    // pairs of the tiles before the current one
+    int used = 0;  // non-empty tiles before the current one
+    TileInfo cur;
+    // The 256 threads go on only together: they meet at named barriers between tiles.
+    bool have = named_barrier_all(1, kMathThreads, tile_take(sm.tiles, 0, cur, abort_flag, p.status, 44));
+    if (lane == 0) tile_release(sm.tiles, 0);
+    if (have) {
+      fetch_rows_and_ids(cur, group);
+      stage_rows(0);
+      fetch_first_size();
+      named_barrier(1, kMathThreads);
+    }
+    for (int seq = 0; have; ++seq) {
+      const int n = cur.count, head = cur.head, qb = cur.block, q_size = cur.aux;
+      const int q_n = covered_rows(q_size);
+      const int pairs = (n + 1) >> 1;
+      const int32_t* list = list_of(cur);
+      // Warpgroup `group` takes the pairs whose running number g0 + i is congruent to it mod 2.
+      for (int i = (g0 ^ group) & 1; i < pairs; i += 2) {
+        const int g = g0 + i;
+        const bool live = (2 * i + tile < n) && key_in_block < size_next;
+        if (p.kv_sizes != nullptr) {
+          if (2 * i + 4 + tile < n) size_next = p.kv_sizes[block_next];
+          if (2 * i + 8 + tile < n) block_next = list[2 * i + 8 + tile];
         }
-        if ((c + 1) * 32 <= q_n)
-          ds_chunk<false>(s_bits, dp_bits, live, c * 32, q_n, sm.neg_lse2, sm.delta, sl2, scale, packed + c * 16);
-        else
-          ds_chunk<true>(s_bits, dp_bits, live, c * 32, q_n, sm.neg_lse2, sm.delta, sl2, scale, packed + c * 16);
-      }
-      // The dQ product of this warpgroup's previous pair has finished reading the dS^T buffer.
-      if (i >= 2) mbar_wait(&sm.ds_free[group], ((i >> 1) - 1) & 1, abort_flag, p.status, 14);
+        mbar_wait(&sm.sp_done[group], (g >> 1) & 1, abort_flag, p.status, 13);
+        tc_fence_after();
+        uint32_t packed[32];
 #pragma unroll
-      for (int c = 0; c < 8; ++c) {
-        if (c * 8 >= q_n) break;  // the product reads q_n queries of every row
-        *reinterpret_cast<uint4*>(ds_row + ((c ^ (key & 7)) << 4)) =
-            make_uint4(packed[4 * c], packed[4 * c + 1], packed[4 * c + 2], packed[4 * c + 3]);
+        for (int c = 0; c < 2; ++c) {
+          if (c * 32 >= q_n) break;  // a short query block has no second half
+          uint32_t s_bits[32], dp_bits[32];
+          VSA_TMEM_LD_32x32b_X32(s_bits, tmem_s + c * 32);
+          VSA_TMEM_LD_32x32b_X32(dp_bits, tmem_s + 64 + c * 32);
+          tmem_wait_ld();
+          if ((c + 1) * 32 >= q_n) {
+            // All of S^T and dP^T is in registers: the accumulators may be overwritten.
+            tc_fence_before();
+            mbar_arrive(&sm.sp_free[group]);
+          }
+          if ((c + 1) * 32 <= q_n)
+            ds_chunk<false>(s_bits, dp_bits, live, c * 32, q_n, sm.neg_lse2, sm.delta, sl2, scale, packed + c * 16);
+          else
+            ds_chunk<true>(s_bits, dp_bits, live, c * 32, q_n, sm.neg_lse2, sm.delta, sl2, scale, packed + c * 16);
+        }
+        // The dQ product of this warpgroup's previous pair has finished reading the dS^T buffer.
+        if (g >= 2) mbar_wait(&sm.ds_free[group], ((g >> 1) - 1) & 1, abort_flag, p.status, 14);
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+          if (c * 8 >= q_n) break;  // the product reads q_n queries of every row
+          *reinterpret_cast<uint4*>(ds_row + ((c ^ (key & 7)) << 4)) =
+              make_uint4(packed[4 * c], packed[4 * c + 1], packed[4 * c + 2], packed[4 * c + 3]);
+        }
+        fence_proxy_async_smem();
+        tc_fence_before();
+        mbar_arrive(&sm.ds_ready[group]);
       }
-      fence_proxy_async_smem();
-      tc_fence_before();
-      mbar_arrive(&sm.ds_ready[group]);
+
+      // The next tile, and the loads it starts with, under this tile's epilogue.
+      TileInfo next;
+      const bool have_next =
+          named_barrier_all(1, kMathThreads, tile_take(sm.tiles, seq + 1, next, abort_flag, p.status, 45));
+      if (lane == 0) tile_release(sm.tiles, seq + 1);
+      if (have_next) fetch_rows_and_ids(next, ((g0 + pairs) ^ group) & 1);
+
+      // -------------------------------------------------------------- epilogue of the tile
+      // Thread = head dim `key`; warpgroup g holds query rows [32g, 32g+32) of dQ^T.  The tile is
+      // turned through shared memory (the dS^T buffers are idle: every dQ product of the tile has
+      // completed) so that global memory sees 16-byte stores of whole row segments; only the
+      // block's valid rows are written.
+      const long long col = static_cast<long long>(head) * kDim + key;
+      // (An empty tile adds nothing to a running FP32 sum.)
+      const bool add_nothing = n == 0 && p.dq_f32 != nullptr && p.f32_accumulate != 0 && cur.aux2 < 0;
+      const bool rows_here = group * 32 < q_size && !add_nothing;
+      // Gradient that reaches the rows through the block's pooled mean, already divided by its size.
+      float term = 0.f;
+      if (cur.aux2 >= 0) {
+        const long long at = static_cast<long long>(cur.aux2) * width + col;
+        term = p.pool_f32 ? static_cast<const float*>(p.dq_pool)[at]
+                          : __bfloat162float(static_cast<const __nv_bfloat16*>(p.dq_pool)[at]);
+        term *= 1.f / static_cast<float>(q_size > 1 ? q_size : 1);
+      }
+      uint32_t bits[32] = {};
+      if (n > 0) {
+        mbar_wait(&sm.dq_final, used & 1, abort_flag, p.status, 16);
+        tc_fence_after();
+        if (rows_here) {
+          VSA_TMEM_LD_32x32b_X32(bits, tmem + lane_base + kColDq + group * 32);
+          tmem_wait_ld();
+        }
+        // dQ^T is in registers (or not needed): the next tile's first dQ product may overwrite it.
+        tc_fence_before();
+        mbar_arrive(&sm.dq_free);
+      }
+      const bool f32_out = p.dq_f32 != nullptr;
+      if (rows_here) {
+        if (f32_out) {
+          float* turn = reinterpret_cast<float*>(sm.ds[0]) + group * 32 * kDim + key;  // [64 rows][128 dims] FP32
+#pragma unroll
+          for (int i = 0; i < 32; ++i) turn[i * kDim] = __uint_as_float(bits[i]) + term;
+        } else {
+          __nv_bfloat16* turn = reinterpret_cast<__nv_bfloat16*>(sm.ds[0]) + group * 32 * kDim + key;  // [64][128] BF16
+#pragma unroll
+          for (int i = 0; i < 32; ++i) turn[i * kDim] = __float2bfloat16(__uint_as_float(bits[i]) + term);
+        }
+      }
+      if (have_next) stage_rows((seq + 1) & 1);  // nobody reads neg_lse2 / delta any more
+      named_barrier(1, kMathThreads);
+      const int math_tid = tid;  // 0..255
+      if (add_nothing) {
+      } else if (f32_out) {
+        // Running FP32 dQ of the ring: rows of 512 bytes, a float4 per thread and step; every old
+        // value is fetched before the first store, so the loads are in flight together.
+        const float4* turn = reinterpret_cast<const float4*>(sm.ds[0]);
+        float4* base = reinterpret_cast<float4*>(p.dq_f32 + static_cast<long long>(qb) * kBlock * width +
+                                                 static_cast<long long>(head) * kDim);
+        const long long row_vecs = width / 4;
+        float4 old[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const int v = math_tid + j * kMathThreads, r = v >> 5, c = v & 31;
+          old[j] = (p.f32_accumulate && r < q_size) ? base[r * row_vecs + c] : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const int v = math_tid + j * kMathThreads, r = v >> 5, c = v & 31;
+          if (r < q_size) {
+            const float4 x = turn[v];
+            base[r * row_vecs + c] = make_float4(old[j].x + x.x, old[j].y + x.y, old[j].z + x.z, old[j].w + x.w);
+          }
+        }
+      } else {
+        const uint4* turn = reinterpret_cast<const uint4*>(sm.ds[0]);
+        const long long* out_row = sm.out_row[seq & 1];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const int v = math_tid + j * kMathThreads, r = v >> 4, c = v & 15;
+          const long long row = out_row[r];
+          if (r < q_size && row >= 0 && row < p.q_out_rows)
+            *reinterpret_cast<uint4*>(p.dq + row * p.out_row_stride + head * p.out_head_stride + c * 8) = turn[v];
+        }
+      }
+      if (have_next) fetch_first_size();
+      // The turning buffer is the next tile's dS^T buffer again.
+      named_barrier(1, kMathThreads);
+      g0 += pairs;
+      if (n > 0) ++used;
+      cur = next;
+      have = have_next;
     }
   }
 
-  // ---------------------------------------------------------------- epilogue
-  if (warp < 8) {
-    if (n > 0) {
-      mbar_wait(&sm.dq_final, 0, abort_flag, p.status, 16);
-      tc_fence_after();
-    }
-    // Thread = head dim `key`; warpgroup g takes query rows [32g, 32g+32), of which only the
-    // block's valid rows are written.  A warp store covers 32 consecutive elements of one row.
-    const long long width = static_cast<long long>(p.heads) * kDim;
-    const long long col = static_cast<long long>(head) * kDim + key;
-    if (group * 32 < q_size) {
-      const float term = pool_term(p.dq_pool, p.pool_f32, p.q_block_coarse, qb, q_size, width, col);
-      uint32_t bits[32] = {};
-      if (n > 0) {
-        VSA_TMEM_LD_32x32b_X32(bits, tmem + lane_base + kColDq + group * 32);
-        tmem_wait_ld();
-      }
-      if (p.dq_f32 != nullptr) {
-        // Running FP32 dQ of the ring: every old value of the chunk is fetched before the first
-        // store, so the loads are in flight together.
-        float* base = p.dq_f32 + (static_cast<long long>(qb) * kBlock + group * 32) * width + col;
-        float old[32];
-#pragma unroll
-        for (int i = 0; i < 32; ++i) old[i] = (p.f32_accumulate && group * 32 + i < q_size) ? base[i * width] : 0.f;
-#pragma unroll
-        for (int i = 0; i < 32; ++i)
-          if (group * 32 + i < q_size) base[i * width] = old[i] + (__uint_as_float(bits[i]) + term);
-      } else {
-#pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const int r = group * 32 + i;
-          const long long row = sm.out_row[r];
-          if (r < q_size && row >= 0 && row < p.q_out_rows)
-            p.dq[row * p.out_row_stride + head * p.out_head_stride + key] = __float2bfloat16(__uint_as_float(bits[i]) + term);
-        }
-      }
-    }
-  }
   tc_fence_before();
   __syncthreads();
   if (warp == 0) tmem_dealloc(tmem, kTmemCols);
@@ -378,8 +559,16 @@ cudaError_t launch_fine_bwd_dq(const FineBwdParams& params, cudaStream_t stream)
   cudaError_t err = cudaFuncSetAttribute(fine_bwd_dq_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          static_cast<int>(smem));
   if (err != cudaSuccess) return err;
-  dim3 grid(params.q_blocks, params.heads);
-  fine_bwd_dq_kernel<<<grid, kThreads, smem, stream>>>(params);
+  // One CTA per SM (a CTA takes a whole SM's shared and tensor memory); fewer when there are fewer tiles.
+  int device = 0, sms = 0;
+  if ((err = cudaGetDevice(&device)) != cudaSuccess) return err;
+  if ((err = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device)) != cudaSuccess) return err;
+  const long long tiles = static_cast<long long>(params.q_blocks) * params.heads;
+  if (tiles <= 0 || tiles > (1LL << 30)) return cudaErrorInvalidValue;
+  FineBwdParams launch = params;
+  if ((err = acquire_tile_counter(stream, &launch.tile_counter)) != cudaSuccess) return err;
+  const unsigned grid = static_cast<unsigned>(tiles < sms ? tiles : sms);
+  fine_bwd_dq_kernel<<<grid, kThreads, smem, stream>>>(launch);
   return cudaGetLastError();
 }
 

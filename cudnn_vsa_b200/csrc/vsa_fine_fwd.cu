@@ -75,20 +75,6 @@ struct FwdSmem {  // placed at a 1024-byte aligned address; every tile offset is
   int abort_flag;
 };
 
-// Position in a ring of three stages / buffers that keeps counting across tiles: `stage` of the
-// next pair, `phase` = parity of that stage's current fill, `round` = fills of stage 0 so far.
-struct Ring3 {
-  int stage = 0, round = 0;
-  uint32_t phase = 0;
-  VSA_DEVICE void advance() {
-    if (++stage == 3) {
-      stage = 0;
-      phase ^= 1;
-      ++round;
-    }
-  }
-};
-
 VSA_DEVICE float fast_exp2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -203,32 +189,42 @@ __global__ void __launch_bounds__(kThreads, 1) fine_fwd_kernel(const __grid_cons
       Ring3 ring;
       int slot = 0;       // kv_size slot of the next pair
       int used = 0;       // non-empty tiles so far
-      // Tile numbers: the block index first, then the work counter; the list length of a tile is
-      // fetched (and the number after it taken) one tile ahead, under the loads of the current one.
+      // Tile numbers: the block index first, then the work counter.  The next number is taken
+      // only when the last loads of the current tile are about to be issued - a CTA that held
+      // tiles in reserve would keep them from idle SMs at the end of the launch, and one list
+      // can be a hundred times longer than another - which still leaves the counter and the list
+      // length a few pairs of time to arrive.
       auto info_of = [&](int t) -> TileInfo {
-        if (t >= tiles) return TileInfo{0, 0, -1, t};
+        if (t >= tiles) return TileInfo{0, 0, -1};
         const int head = t / p.q_blocks, qb = t - head * p.q_blocks;
-        return TileInfo{head, qb, p.counts[static_cast<long long>(head) * p.count_head_stride + qb], t};
+        const long long row = static_cast<long long>(head) * p.count_head_stride + qb;
+        if (p.list_bounds == nullptr) return TileInfo{head, qb, p.counts[row], 0};
+        // aux = first entry of the list's sub-range
+        const int32_t* bounds = p.list_bounds + row * p.bounds_stride;
+        const int begin = bounds[0];
+        return TileInfo{head, qb, bounds[1] - begin, begin};
       };
       auto take_number = [&]() -> int { return static_cast<int>(gridDim.x + atomicAdd(p.tile_counter, 1u)); };
       TileInfo cur = info_of(static_cast<int>(blockIdx.x));
-      int t_next = cur.count >= 0 ? take_number() : tiles;
       for (int seq = 0;; ++seq) {
         tile_publish(sm.tiles, seq, cur, abort_flag, p.status, 33);
         if (cur.count < 0 || *abort_flag) break;  // end of the tiles, or a wait gave up: start no further loads
-        const TileInfo next = info_of(t_next);
-        t_next = next.count >= 0 ? take_number() : tiles;
         const int n = cur.count, head = cur.head, qb = cur.block;
-        cur = next;
-        if (n == 0) continue;
+        if (n == 0) {
+          cur = info_of(take_number());
+          continue;
+        }
         const int32_t* list = p.indices + static_cast<long long>(head) * p.index_head_stride +
-                              static_cast<long long>(qb) * p.capacity;
+                              static_cast<long long>(qb) * p.capacity + cur.aux;
         const int pairs = (n + 1) >> 1, qbuf = used & 1;
+        const int claim_at = pairs > kStages ? pairs - kStages : 0;
         // The Q buffer was last read by the S products of the tile before the previous one.
         if (used >= 2) mbar_wait(&sm.q_free[qbuf], ((used >> 1) - 1) & 1, abort_flag, p.status, 31);
         mbar_expect_tx(&sm.q_full[qbuf], kTileBytes);
         tma_load_tile(sm.q[qbuf], &p.q_map, &sm.q_full[qbuf], head, qb);
+        int t_next = tiles;
         for (int i = 0; i < pairs; ++i) {
+          if (i == claim_at) t_next = take_number();
           const int count = (2 * i + 1 < n) ? 2 : 1;
           const int stage = ring.stage;
           // The valid length of each block travels with the stage: the softmax threads read it from
@@ -253,6 +249,7 @@ __global__ void __launch_bounds__(kThreads, 1) fine_fwd_kernel(const __grid_cons
           if (++slot == 2 * kStages) slot = 0;
         }
         ++used;
+        cur = info_of(t_next);
       }
     }
   } else if (warp == 10) {
@@ -265,7 +262,7 @@ __global__ void __launch_bounds__(kThreads, 1) fine_fwd_kernel(const __grid_cons
         const int n = info.count, head = info.head, qb = info.block;
         if (n == 0) continue;
         const int32_t* list = p.indices + static_cast<long long>(head) * p.index_head_stride +
-                              static_cast<long long>(qb) * p.capacity;
+                              static_cast<long long>(qb) * p.capacity + info.aux;
         const int pairs = (n + 1) >> 1;
         for (int i = 0; i < pairs; ++i) {
           const int count = (2 * i + 1 < n) ? 2 : 1;

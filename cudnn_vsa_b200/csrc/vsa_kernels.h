@@ -20,6 +20,10 @@ struct FineFwdParams {
   long long index_head_stride;      // elements between heads (0 = one table for all heads)
   long long count_head_stride;
   int capacity;
+  // Optional sub-range of every list: row r = head * count_head_stride + block uses the entries
+  // [list_bounds[r * bounds_stride], list_bounds[r * bounds_stride + 1]) and `counts` is ignored.
+  const int32_t* list_bounds;
+  int bounds_stride;
   const int32_t* kv_sizes;          // [kv_blocks] valid slots per KV block, or null (all 64)
   __nv_bfloat16* o_slots;           // [q_slots, heads, 128] normalised fine output
   float* lse;                       // [heads, q_slots]
@@ -51,6 +55,12 @@ struct FineBwdParams {
   const int32_t* counts;
   long long index_head_stride, count_head_stride;
   int capacity;
+  // dQ kernel, optional sub-range of every list: row r = head * count_head_stride + block uses the
+  // entries [list_bounds[r * bounds_stride], list_bounds[r * bounds_stride + 1]), not `counts`.
+  const int32_t* list_bounds;
+  int bounds_stride;
+  // dK/dV kernel: only the query blocks of mask words [mask_word_begin, mask_word_end) are walked.
+  int mask_word_begin, mask_word_end;
   const int32_t* kv_sizes;      // [kv_blocks] or null
   const float* lse;             // [heads, q_slots]
   const float* delta;           // [heads, q_slots] rowsum(dO * O)
@@ -90,6 +100,7 @@ struct FineBwdParams {
   int q_blocks, kv_blocks, heads;
   float scale;
   int* status;
+  unsigned* tile_counter;  // set by each launcher
 };
 cudaError_t launch_fine_bwd_dq(const FineBwdParams& params, cudaStream_t stream);
 cudaError_t launch_fine_bwd_dkv(const FineBwdParams& params, cudaStream_t stream);
@@ -172,6 +183,8 @@ cudaError_t launch_partition_indices(const int32_t* index, const int32_t* counts
                                      int32_t* out_lists, int32_t* out_counts, long long rows, int capacity,
                                      int out_capacity, int ring_size, int peer_blocks, long long list_stride,
                                      long long count_stride, cudaStream_t stream);
+cudaError_t launch_list_bounds(const int32_t* lists, const int32_t* counts, long long rows, int capacity,
+                               int chunk_blocks, int chunks, int32_t* bounds, cudaStream_t stream);
 cudaError_t launch_merge_partial(float* out, float* lse, const __nv_bfloat16* part, const float* part_lse,
                                  long long slots, int heads, cudaStream_t stream);
 

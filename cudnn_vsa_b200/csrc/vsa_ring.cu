@@ -56,6 +56,30 @@ __global__ void __launch_bounds__(kPartThreads) partition_kernel(
   for (int i = s_total + threadIdx.x; i < out_capacity; i += kPartThreads) dst[i] = 0;
 }
 
+// bounds[row][c] = first position of the row's ascending list whose block id is >= c * chunk_blocks
+// (c = 0 .. chunks - 1); bounds[row][chunks] = the row's count.  One thread per (row, c).
+__global__ void list_bounds_kernel(const int32_t* __restrict__ lists, const int32_t* __restrict__ counts,
+                                   long long rows, int capacity, int chunk_blocks, int chunks,
+                                   int32_t* __restrict__ bounds) {
+  const long long id = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  const long long row = id / (chunks + 1);
+  const int c = static_cast<int>(id - row * (chunks + 1));
+  if (row >= rows) return;
+  const int n = min(counts[row], capacity);
+  int lo = 0, hi = n;
+  if (c < chunks) {
+    const long long first = static_cast<long long>(c) * chunk_blocks;
+    const int32_t* list = lists + row * capacity;
+    while (lo < hi) {
+      const int mid = (lo + hi) >> 1;
+      if (list[mid] < first) lo = mid + 1; else hi = mid;
+    }
+  } else {
+    lo = n;
+  }
+  bounds[row * (chunks + 1) + c] = lo;
+}
+
 __global__ void merge_partial_kernel(float* __restrict__ out, float* __restrict__ lse,
                                      const __nv_bfloat16* __restrict__ part, const float* __restrict__ part_lse,
                                      long long slots, int heads) {
@@ -95,6 +119,15 @@ cudaError_t launch_partition_indices(const int32_t* index, const int32_t* counts
   dim3 grid(static_cast<unsigned>(rows), ring_size);
   partition_kernel<<<grid, kPartThreads, 0, stream>>>(index, counts, global_to_gather, out_lists, out_counts, capacity,
                                                       out_capacity, peer_blocks, list_stride, count_stride);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_list_bounds(const int32_t* lists, const int32_t* counts, long long rows, int capacity,
+                               int chunk_blocks, int chunks, int32_t* bounds, cudaStream_t stream) {
+  const long long threads = rows * (chunks + 1);
+  if (threads == 0) return cudaSuccess;
+  list_bounds_kernel<<<static_cast<unsigned>((threads + 255) / 256), 256, 0, stream>>>(lists, counts, rows, capacity,
+                                                                                      chunk_blocks, chunks, bounds);
   return cudaGetLastError();
 }
 

@@ -15,6 +15,14 @@ dQ) under it, joins, and then runs the dK/dV kernel, which adds this rank's cont
 straight into the buffer that just arrived; after ``R`` steps the sums are home.  No per-step
 allocation, no separate accumulation pass.  Collectives are NCCL through the borrowed process
 group; a remote shard always lands in this GPU's memory before any kernel reads it.
+
+A step whose shard is larger than ``RING_CHUNK_BLOCKS`` blocks is run in passes.  K and V of one
+head of such a shard do not fit the L2 cache, every CTA then streams its listed blocks from DRAM
+and the SM clock drops under the power cap; a pass restricts all lists to one KV range of the
+shard (lists are ascending, so that is a contiguous sub-range of each list, found once per call
+by ``vsa_list_bounds``), which keeps the CTAs that run together on the same cache-resident part.
+The forward and the dQ kernels take KV ranges; the dK/dV kernel, whose streaming side is Q and dO,
+takes ranges of query blocks and adds the passes up in the FP32 sums.
 """
 from __future__ import annotations
 
@@ -26,6 +34,11 @@ import torch.distributed as dist
 from . import _cabi
 from .vsa_core import _fine_fwd, _p, device_plan, route
 from .vsa_layout import BLOCK
+
+
+# Largest number of 64-slot blocks one pass of a ring step covers (K and V of a head: 32 KiB per
+# block, 64 MiB for 2048 blocks - about half of the L2 cache).
+RING_CHUNK_BLOCKS = 2048
 
 
 @dataclass
@@ -137,6 +150,26 @@ def partition(index, counts, layout, runtime):
             numbers[:, :rows].view(runtime.size, heads, blocks))
 
 
+def _passes(blocks):
+    """Number of passes and blocks per pass for a range of `blocks` blocks."""
+    count = max(1, -(-blocks // RING_CHUNK_BLOCKS))
+    return count, -(-blocks // count)
+
+
+def list_bounds(lists, counts, kv_blocks):
+    """``(bounds [R, H, C, passes + 1] or None, passes)``: where each KV range of a shard starts in
+    every per-owner list."""
+    passes, chunk = _passes(kv_blocks)
+    if passes == 1:
+        return None, 1
+    owners, heads, blocks, cap = lists.shape
+    bounds = torch.empty((owners, heads, blocks, passes + 1), dtype=torch.int32, device=lists.device)
+    for owner in range(owners):
+        _cabi.call("vsa_list_bounds", _p(lists[owner]), _p(counts[owner]), heads * blocks, cap, chunk, passes,
+                   _p(bounds[owner]), _cabi.stream())
+    return bounds, passes
+
+
 def _gather_rows(x, row_map):
     out = torch.empty((row_map.numel(), *x.shape[1:]), dtype=x.dtype, device=x.device)
     if out.numel():
@@ -146,13 +179,36 @@ def _gather_rows(x, row_map):
 
 
 def _bwd_call(q, k, v, d_o, index, counts, sizes_q, sizes_kv, scale, lse, delta, mask, status, *, parts,
-              dq=None, dk=None, dv=None, dq_f32=None, dk_f32=None, dv_f32=None, accumulate=0, early_kv=0):
+              dq=None, dk=None, dv=None, dq_f32=None, dk_f32=None, dv_f32=None, accumulate=0, early_kv=0,
+              bounds=None, passes=1):
+    """One ring step of the dQ kernel (parts = 3: mask, then dQ) or of the dK/dV kernel (parts = 4),
+    in passes over KV ranges / query-block ranges when the shard is large."""
     heads = q.shape[1]
-    parts |= int(early_kv) << 8  # scheduling hint of the dK/dV kernel
+    hint = int(early_kv) << 8  # scheduling hint of the dK/dV kernel
     q_blocks, kv_blocks = q.shape[0] // BLOCK, k.shape[0] // BLOCK
+    words = _cabi.load().vsa_kv_mask_words(q_blocks)
+    q_passes, _ = _passes(q_blocks)
     with _cabi.mark("ring_step_dq" if parts & 2 else "ring_step_dkv"):
-        _bwd_launch(q, k, v, d_o, index, counts, sizes_q, sizes_kv, scale, lse, delta, mask, status, parts, dq, dk,
-                    dv, dq_f32, dk_f32, dv_f32, accumulate, heads, q_blocks, kv_blocks)
+        if parts & 2 and bounds is None or parts & 4 and q_passes == 1:
+            _bwd_launch(q, k, v, d_o, index, counts, sizes_q, sizes_kv, scale, lse, delta, mask, status, parts | hint,
+                        dq, dk, dv, dq_f32, dk_f32, dv_f32, accumulate, heads, q_blocks, kv_blocks)
+            return
+
+        def launch(now, bound, stride, word_begin, word_end, add):
+            _cabi.call("vsa_fine_bwd_range", _p(q), _p(k), _p(v), _p(d_o), q_blocks, kv_blocks, heads, _p(index),
+                       _p(counts), _p(bound), index.stride(0), counts.stride(0), stride, index.shape[-1], _p(sizes_q),
+                       _p(sizes_kv), scale, _p(lse), _p(delta), _p(mask), word_begin, word_end, _p(dq_f32),
+                       _p(dk_f32), _p(dv_f32), add, now, _p(status), _cabi.stream(),
+                       launches=bin(now & 7).count("1"))
+
+        if parts & 2:
+            flat = bounds.flatten()
+            for c in range(passes):
+                launch((parts & 1 if c == 0 else 0) | 2, flat[c:], passes + 1, 0, words, accumulate)
+        else:
+            per = -(-words // q_passes)  # whole 32-block mask words per pass
+            for begin in range(0, words, per):
+                launch(4 | hint, None, 0, begin, min(words, begin + per), 1 if (accumulate or begin) else 0)
 
 
 def _bwd_launch(q, k, v, d_o, index, counts, sizes_q, sizes_kv, scale, lse, delta, mask, status, parts, dq, dk, dv,
@@ -185,6 +241,7 @@ class _RingVSAFunction(torch.autograd.Function):
             k_all, v_all = gather_means(mean[1], mean[2], rt, ring.global_to_gather)
             index = route(mean[0], k_all, layout, plan)
         lists, counts = partition(index, layout.routing_counts, layout, rt)
+        bounds, passes = list_bounds(lists, counts, kv.shape[1] // BLOCK)
 
         out_f32 = torch.zeros((slots, heads, dim), dtype=torch.float32, device=q.device)
         lse = torch.full((heads, slots), float("-inf"), dtype=torch.float32, device=q.device)
@@ -195,10 +252,18 @@ class _RingVSAFunction(torch.autograd.Function):
             current = buffers[step % len(buffers)]
             if step + 1 < rt.size:
                 ring_exchange(rt, [(current, buffers[(step + 1) % 2])])
-            _cabi.call("vsa_fine_fwd_running", _p(q_s), _p(current[0]), _p(current[1]), blocks,
-                       current.shape[1] // BLOCK, heads, _p(lists[owner]), _p(counts[owner]), lists.stride(1),
-                       counts.stride(1), lists.shape[-1], _p(ring.peer_block_sizes[owner]), scale, _p(out_f32),
-                       _p(lse), _p(plan.status), _cabi.stream())
+            if bounds is None:
+                _cabi.call("vsa_fine_fwd_running", _p(q_s), _p(current[0]), _p(current[1]), blocks,
+                           current.shape[1] // BLOCK, heads, _p(lists[owner]), _p(counts[owner]), lists.stride(1),
+                           counts.stride(1), lists.shape[-1], _p(ring.peer_block_sizes[owner]), scale, _p(out_f32),
+                           _p(lse), _p(plan.status), _cabi.stream())
+            else:
+                flat = bounds[owner].flatten()
+                for c in range(passes):
+                    _cabi.call("vsa_fine_fwd_running_range", _p(q_s), _p(current[0]), _p(current[1]), blocks,
+                               current.shape[1] // BLOCK, heads, _p(lists[owner]), _p(flat[c:]), lists.stride(1),
+                               counts.stride(1), passes + 1, lists.shape[-1], _p(ring.peer_block_sizes[owner]),
+                               scale, _p(out_f32), _p(lse), _p(plan.status), _cabi.stream())
             if step + 1 < rt.size:
                 join_exchange(rt)
 
@@ -216,6 +281,7 @@ class _RingVSAFunction(torch.autograd.Function):
         ctx.save_for_backward(q_s, current, o_s, lse, lists, counts, gate if coarse_o is not None else None,
                               coarse_o, coarse_lse, *(tok if tok is not None else (None, None, None)))
         ctx.layout, ctx.scale, ctx.runtime = layout, scale, rt
+        ctx.bounds, ctx.passes = bounds, passes
         return out
 
     @staticmethod
@@ -287,7 +353,8 @@ class _RingVSAFunction(torch.autograd.Function):
                 ring_exchange(rt, pairs, reverse=True)
             common = (q_s, current[0], current[1], grad_s, lists[owner], counts[owner], layout.block_sizes,
                       ring.peer_block_sizes[owner], scale, lse, delta, mask, plan.status)
-            _bwd_call(*common, parts=3, dq_f32=dq_acc, accumulate=1)
+            _bwd_call(*common, parts=3, dq_f32=dq_acc, accumulate=1,
+                      bounds=None if ctx.bounds is None else ctx.bounds[owner], passes=ctx.passes)
             if pairs:
                 join_exchange(rt)
             _bwd_call(*common, parts=4, dk_f32=target[0], dv_f32=target[1], accumulate=1 if step else 0,

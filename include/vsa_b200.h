@@ -206,6 +206,36 @@ int vsa_fine_bwd_strided(const void* q, const void* k, const void* v, const void
                          int32_t pool_f32, const int32_t* q_block_coarse, const int32_t* kv_block_coarse,
                          int32_t parts, int32_t* status, void* stream);
 
+/* Ring step in passes over sub-ranges of the shard.  A shard whose K and V of one head exceed the
+ * L2 cache is walked in `chunks` passes of `chunk_blocks` KV blocks each, so that the CTAs that run
+ * together read the same cache-resident part of it; lists are ascending, so the entries of one
+ * pass are a contiguous sub-range of every list.
+ *   vsa_list_bounds: bounds [rows, chunks + 1] int32; bounds[r][c] = first position of row r whose
+ *     block id is >= c * chunk_blocks, bounds[r][chunks] = counts[r].  lists [rows, capacity].
+ *   vsa_fine_fwd_running_range: vsa_fine_fwd_running on the entries [b[0], b[1]) of every list, with
+ *     b = list_bounds + (head * count_head_stride + block) * bounds_stride (pass `bounds + c` for
+ *     pass c and bounds_stride = chunks + 1).
+ *   vsa_fine_bwd_range: vsa_fine_bwd with FP32 results only (ring form).  parts & 1 builds the mask
+ *     from the whole lists (`counts`); parts & 2 runs the dQ kernel on the list sub-range (null
+ *     list_bounds = whole lists); parts & 4 runs the dK/dV kernel over the query blocks of mask
+ *     words [mask_word_begin, mask_word_end) only (32 query blocks per word; the passes of one
+ *     step add into dk_f32 / dv_f32 with f32_accumulate = 1 after the first).
+ * No counterpart in the reference, whose ring step is one cuDNN call per shard (vsa_core.py:234-240). */
+int vsa_list_bounds(const int32_t* lists, const int32_t* counts, int64_t rows, int32_t capacity, int32_t chunk_blocks,
+                    int32_t chunks, int32_t* bounds, void* stream);
+int vsa_fine_fwd_running_range(const void* q, const void* k, const void* v, int64_t q_blocks, int64_t kv_blocks,
+                               int32_t heads, const int32_t* indices, const int32_t* list_bounds,
+                               int64_t index_head_stride, int64_t count_head_stride, int32_t bounds_stride,
+                               int32_t capacity, const int32_t* kv_sizes, float scale, float* o_running,
+                               float* lse_running, int32_t* status, void* stream);
+int vsa_fine_bwd_range(const void* q, const void* k, const void* v, const void* d_o, int64_t q_blocks,
+                       int64_t kv_blocks, int32_t heads, const int32_t* indices, const int32_t* counts,
+                       const int32_t* list_bounds, int64_t index_head_stride, int64_t count_head_stride,
+                       int32_t bounds_stride, int32_t capacity, const int32_t* q_sizes, const int32_t* kv_sizes,
+                       float scale, const float* lse, const float* delta, uint32_t* kv_mask, int32_t mask_word_begin,
+                       int32_t mask_word_end, float* dq_f32, float* dk_f32, float* dv_f32, int32_t f32_accumulate,
+                       int32_t parts, int32_t* status, void* stream);
+
 /* Ring: split routing rows into per-owner lists of owner-local block ids.
  *   index [rows, capacity], counts [rows], global_to_gather [global blocks] int64.
  *   out_lists [ring_size][list_stride] holds rows of `out_capacity` ids, out_counts

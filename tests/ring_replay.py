@@ -1,6 +1,7 @@
 """One rank's ring step on a single GPU, without transport: timing and profiling of the ring path.
 
     python tests/ring_replay.py [--ring R] [--workload NAME] [--heads H] [--steps K] [--separate-merge]
+                                [--chunk-blocks B]
 
 Builds rank 0's shard of an R-rank ring layout from a backend-free process group and runs
 ``vsa_attention`` on it with the three collectives replaced by local stand-ins: a ring hop is a
@@ -12,6 +13,9 @@ captures are representative; the VALUES are not those of a real ring (every peer
 this rank's data) and nothing here checks them - parity of the ring path is checked by
 ``tests/ring_worker.py`` on real NCCL ranks and by ``tests/test_gpu_ring.py``.  Prints one JSON
 line with the step time and the device time per C entry point.
+
+``--chunk-blocks`` sets the number of blocks one pass of a ring step covers (default: the
+library's ``RING_CHUNK_BLOCKS``; a value above the shard size gives one pass per step).
 
 ``--separate-merge`` also runs, per forward step, the plain forward kernel followed by the
 stand-alone partial-merge kernel (the unfused form of the same step), so that kernel can be
@@ -41,7 +45,10 @@ def main():
     parser.add_argument("--heads", type=int, default=None)
     parser.add_argument("--steps", type=int, default=2)
     parser.add_argument("--separate-merge", action="store_true")
+    parser.add_argument("--chunk-blocks", type=int, default=None)
     args = parser.parse_args()
+    if args.chunk_blocks:
+        vsa_ring.RING_CHUNK_BLOCKS = args.chunk_blocks
     samples, heads, _, _ = bench.WORKLOADS[args.workload]
     heads = args.heads or heads
     ring = args.ring
@@ -110,6 +117,7 @@ def main():
     spans = tr.summary()
     vsa_core.check_status(layout)
     print(json.dumps({"ring": ring, "workload": args.workload, "heads": heads, "local_blocks": layout.blocks,
+                      "chunk_blocks": vsa_ring.RING_CHUNK_BLOCKS,
                       "global_tokens": full.tokens, "ms_per_step": start.elapsed_time(stop) / args.steps,
                       "entry_points_ms": {k: [round(v["ms"], 3), v["calls"]]
                                           for k, v in sorted(spans.items(), key=lambda kv: -kv[1]["ms"])}}))

@@ -151,7 +151,12 @@ def test_partial_merge_with_empty_steps():
     torch.testing.assert_close(lse.double().cpu(), want_lse, atol=2e-6, rtol=2e-6)
 
 
-def test_size_one_ring_group_matches_single_device():
+@pytest.mark.parametrize("chunk", [None, 16, 5])
+def test_size_one_ring_group_matches_single_device(chunk, monkeypatch):
+    """chunk: blocks per pass of a ring step (None = default, one pass here).  16 gives three KV
+    passes and two query-block passes of one mask word each on the 33 blocks; 5 gives seven."""
+    if chunk is not None:
+        monkeypatch.setattr(vsa_ring, "RING_CHUNK_BLOCKS", chunk)
     if not dist.is_initialized():
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         os.environ.setdefault("MASTER_PORT", "29581")
