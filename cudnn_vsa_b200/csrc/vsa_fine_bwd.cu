@@ -115,15 +115,21 @@ struct DkvSmem {  // placed at a 1024-byte aligned address; every tile offset is
 // Walks the set bits of one (head, KV block) row of the query-block bitmask in ascending order.
 // Every thread that needs the sequence keeps its own cursor, so nothing is passed through
 // shared memory.
+// The two words after the current one are already on their way when the current one runs out, so
+// stepping to the next word does not wait for memory (a row has a few set bits per word).
 struct MaskCursor {
   const uint32_t* words;  // the whole row
   int end, word;          // walks words [first, end)
-  uint32_t bits;
-  VSA_DEVICE MaskCursor(const uint32_t* w, int first, int e) : words(w), end(e), word(first), bits(first < e ? w[first] : 0u) {}
+  uint32_t bits, ahead1, ahead2;
+  VSA_DEVICE MaskCursor(const uint32_t* w, int first, int e)
+      : words(w), end(e), word(first), bits(first < e ? w[first] : 0u), ahead1(first + 1 < e ? w[first + 1] : 0u),
+        ahead2(first + 2 < e ? w[first + 2] : 0u) {}
   VSA_DEVICE int next() {
     while (bits == 0) {
       if (++word >= end) return 0;
-      bits = words[word];
+      bits = ahead1;
+      ahead1 = ahead2;
+      ahead2 = word + 2 < end ? words[word + 2] : 0u;
     }
     const int bit = __ffs(bits) - 1;
     bits &= bits - 1;
@@ -209,8 +215,11 @@ __global__ void __launch_bounds__(kDkvThreads, 1) fine_bwd_dkv_kernel(const __gr
   const int group = (warp >> 2) & 1;  // score-math warpgroup (warps 0..7 only)
   const int qrow = tid & 127;         // query row of the pair owned by this thread (math role) / head dim (epilogue)
   const uint32_t* mask = p.kv_mask + (static_cast<long long>(head) * p.kv_blocks + kvb) * p.mask_words;
+  // Listed query blocks of this tile: every warp counts the row's bits, a few words per lane.
   int n = 0;
-  for (int w = p.mask_word_begin; w < p.mask_word_end; ++w) n += __popc(mask[w]);
+  for (int w = p.mask_word_begin + lane; w < p.mask_word_end; w += 32) n += __popc(mask[w]);
+#pragma unroll
+  for (int shift = 16; shift > 0; shift >>= 1) n += __shfl_xor_sync(0xffffffffu, n, shift);
 
   if (tid == 0) {
     mbar_init(&sm.kv_full, 1);
