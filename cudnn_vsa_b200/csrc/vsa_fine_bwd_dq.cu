@@ -15,10 +15,13 @@
 // sit in shared memory (pre-scaled) and are read as broadcasts.  P is recomputed from the saved
 // LSE (natural log), dS^T = P^T * (dP^T - delta) * scale is written as BF16 rows [key][query],
 // which is directly the MN-major B operand of the third product; K^T is the K pair read MN-major.
-// Two warpgroups take alternate pairs, each with its own S^T / dP^T accumulators and dS^T buffer,
-// one warp issues the score products and another the dQ products, synchronised only through
-// mbarriers, so the exponentials of one pair run under the products of its neighbours and a wait
-// of one kind of product never holds up the other.  K pair stages are
+// Both score-math warpgroups work on every pair - a thread owns one key and 32 of the 64 queries -
+// because the latency of that step is on the critical path: a K stage is only refilled after the
+// pair's dQ product, which waits for the pair's dS^T, and there is room for three K stages.  Two
+// sets of S^T / dP^T accumulators and two dS^T buffers alternate between pairs; one warp issues
+// the score products and another the dQ products, synchronised only through mbarriers, so the
+// exponentials of one pair run under the products of its neighbours and a wait of one kind of
+// product never holds up the other.  K pair stages are
 // held until their dQ product has read them (three stages), V pair stages only until dP^T (two).
 // The epilogue adds the gradient that reaches a row through its block's pooled mean and scatters
 // the rows to the caller's row order, skipping padding slots (reference vsa_core.py:23-30, 42-47;
@@ -31,8 +34,7 @@ namespace vsa {
 
 namespace {
 
-constexpr int kGroupThreads = 128;  // one score-math warpgroup
-constexpr int kMathThreads = 256;   // warps 0..3: warpgroup 0 (even pairs), warps 4..7: warpgroup 1 (odd pairs)
+constexpr int kMathThreads = 256;   // warps 0..3 / 4..7: queries 0..31 / 32..63 of every pair's S^T and dP^T
 constexpr int kThreads = 384;       // warp 8: issues the dQ products, warps 9 / 10: TMA loads of Q, dO, K / of V, warp 11: issues the score products
 constexpr int kTmemCols = 512;      // per warpgroup g: S^T [128g, 128g+64)  dP^T [128g+64, 128g+128);  dQ^T [256,320)
 constexpr uint32_t kColDq = 256;
@@ -149,8 +151,8 @@ __global__ void __launch_bounds__(kThreads, 1) fine_bwd_dq_kernel(const __grid_c
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(&sm.sp_done[i], 1);
-      mbar_init(&sm.sp_free[i], kGroupThreads);
-      mbar_init(&sm.ds_ready[i], kGroupThreads);
+      mbar_init(&sm.sp_free[i], kMathThreads);
+      mbar_init(&sm.ds_ready[i], kMathThreads);
       mbar_init(&sm.ds_free[i], 1);
     }
     mbar_init(&sm.dq_final, 1);
@@ -356,8 +358,8 @@ __global__ void __launch_bounds__(kThreads, 1) fine_bwd_dq_kernel(const __grid_c
     }
   } else {
     // ------------------------------------------------------------ score math warpgroups and epilogue
-    const uint32_t tmem_s = tmem + lane_base + group * 128;
-    uint8_t* ds_row = sm.ds[group] + key * 128;
+    // Thread = key `key` of the pair (TMEM lane); warpgroup `group` takes queries [32 group, 32 group + 32).
+    uint8_t* ds_row0 = sm.ds[0] + key * 128;
     const int tile = key >> 6, key_in_block = key & 63;
     const float scale = p.scale, sl2 = p.scale * kLog2eBwd;
     const long long width = static_cast<long long>(p.heads) * kDim;
@@ -366,14 +368,14 @@ __global__ void __launch_bounds__(kThreads, 1) fine_bwd_dq_kernel(const __grid_c
     // LSE, delta and output row of query row `tid` (threads 0..63) into registers, staged into
     // shared memory before the epilogue's first barrier, and the first steps of the block-size
     // lookups below.  The valid length of a block comes from two dependent global loads (list,
-    // then sizes); they are software-pipelined over two rounds - the block id is fetched two
-    // rounds ahead, the size one round ahead from an id that is already in a register - so no
+    // then sizes); they are software-pipelined over two pairs - the block id is fetched two
+    // pairs ahead, the size one pair ahead from an id that is already in a register - so no
     // load is issued behind the one it depends on.  Between tiles the ids are fetched before
     // the epilogue and the first size after it.
     float pre_lse = 0.f, pre_delta = 0.f;
     long long pre_row = 0;
     int size_next = kBlock, block_next = 0, block_first = -1;
-    auto fetch_rows_and_ids = [&](const TileInfo& t, int first_pair) {
+    auto fetch_rows_and_ids = [&](const TileInfo& t) {
       if (tid < kBlock) {
         const long long s = static_cast<long long>(t.block) * kBlock + tid;
         pre_row = p.q_slot_row != nullptr ? p.q_slot_row[s] : s;
@@ -384,8 +386,8 @@ __global__ void __launch_bounds__(kThreads, 1) fine_bwd_dq_kernel(const __grid_c
       block_first = -1;
       block_next = 0;
       if (p.kv_sizes != nullptr) {
-        if (2 * first_pair + tile < t.count) block_first = list[2 * first_pair + tile];
-        if (2 * first_pair + 4 + tile < t.count) block_next = list[2 * first_pair + 4 + tile];
+        if (tile < t.count) block_first = list[tile];
+        if (2 + tile < t.count) block_next = list[2 + tile];
       }
     };
     auto stage_rows = [&](int parity) {
@@ -404,7 +406,7 @@ __global__ void __launch_bounds__(kThreads, 1) fine_bwd_dq_kernel(const __grid_c
     bool have = named_barrier_all(1, kMathThreads, tile_take(sm.tiles, 0, cur, abort_flag, p.status, 44));
     if (lane == 0) tile_release(sm.tiles, 0);
     if (have) {
-      fetch_rows_and_ids(cur, group);
+      fetch_rows_and_ids(cur);
       stage_rows(0);
       fetch_first_size();
       named_barrier(1, kMathThreads);
@@ -414,45 +416,49 @@ __global__ void __launch_bounds__(kThreads, 1) fine_bwd_dq_kernel(const __grid_c
       const int q_n = covered_rows(q_size);
       const int pairs = (n + 1) >> 1;
       const int32_t* list = list_of(cur);
-      // Warpgroup `group` takes the pairs whose running number g0 + i is congruent to it mod 2.
-      for (int i = (g0 ^ group) & 1; i < pairs; i += 2) {
-        const int g = g0 + i;
+      // This warpgroup's queries: none when the block is that short, else all 32 or a masked chunk.
+      const bool has_queries = group * 32 < q_n, full_chunk = (group + 1) * 32 <= q_n;
+      for (int i = 0; i < pairs; ++i) {
+        const int g = g0 + i, set = g & 1;
         const bool live = (2 * i + tile < n) && key_in_block < size_next;
         if (p.kv_sizes != nullptr) {
-          if (2 * i + 4 + tile < n) size_next = p.kv_sizes[block_next];
-          if (2 * i + 8 + tile < n) block_next = list[2 * i + 8 + tile];
+          if (2 * i + 2 + tile < n) size_next = p.kv_sizes[block_next];
+          if (2 * i + 4 + tile < n) block_next = list[2 * i + 4 + tile];
         }
-        mbar_wait(&sm.sp_done[group], (g >> 1) & 1, abort_flag, p.status, 13);
+        mbar_wait(&sm.sp_done[set], (g >> 1) & 1, abort_flag, p.status, 13);
         tc_fence_after();
-        uint32_t packed[32];
-#pragma unroll
-        for (int c = 0; c < 2; ++c) {
-          if (c * 32 >= q_n) break;  // a short query block has no second half
+        uint32_t packed[16];
+        if (has_queries) {
           uint32_t s_bits[32], dp_bits[32];
-          VSA_TMEM_LD_32x32b_X32(s_bits, tmem_s + c * 32);
-          VSA_TMEM_LD_32x32b_X32(dp_bits, tmem_s + 64 + c * 32);
+          const uint32_t tmem_s = tmem + lane_base + set * 128 + group * 32;
+          VSA_TMEM_LD_32x32b_X32(s_bits, tmem_s);
+          VSA_TMEM_LD_32x32b_X32(dp_bits, tmem_s + 64);
           tmem_wait_ld();
-          if ((c + 1) * 32 >= q_n) {
-            // All of S^T and dP^T is in registers: the accumulators may be overwritten.
-            tc_fence_before();
-            mbar_arrive(&sm.sp_free[group]);
-          }
-          if ((c + 1) * 32 <= q_n)
-            ds_chunk<false>(s_bits, dp_bits, live, c * 32, q_n, sm.neg_lse2, sm.delta, sl2, scale, packed + c * 16);
+          // This thread's part of S^T and dP^T is in registers: the accumulators may be overwritten
+          // once all 256 threads have said so.
+          tc_fence_before();
+          mbar_arrive(&sm.sp_free[set]);
+          if (full_chunk)
+            ds_chunk<false>(s_bits, dp_bits, live, group * 32, q_n, sm.neg_lse2, sm.delta, sl2, scale, packed);
           else
-            ds_chunk<true>(s_bits, dp_bits, live, c * 32, q_n, sm.neg_lse2, sm.delta, sl2, scale, packed + c * 16);
+            ds_chunk<true>(s_bits, dp_bits, live, group * 32, q_n, sm.neg_lse2, sm.delta, sl2, scale, packed);
+        } else {
+          mbar_arrive(&sm.sp_free[set]);
         }
-        // The dQ product of this warpgroup's previous pair has finished reading the dS^T buffer.
-        if (g >= 2) mbar_wait(&sm.ds_free[group], ((g >> 1) - 1) & 1, abort_flag, p.status, 14);
+        // The dQ product of the pair before last has finished reading this dS^T buffer.
+        if (g >= 2) mbar_wait(&sm.ds_free[set], ((g >> 1) - 1) & 1, abort_flag, p.status, 14);
+        if (has_queries) {
+          uint8_t* ds_row = ds_row0 + set * kTileBytes;
 #pragma unroll
-        for (int c = 0; c < 8; ++c) {
-          if (c * 8 >= q_n) break;  // the product reads q_n queries of every row
-          *reinterpret_cast<uint4*>(ds_row + ((c ^ (key & 7)) << 4)) =
-              make_uint4(packed[4 * c], packed[4 * c + 1], packed[4 * c + 2], packed[4 * c + 3]);
+          for (int c = 0; c < 4; ++c) {
+            if ((group * 4 + c) * 8 >= q_n) break;  // the product reads q_n queries of every row
+            *reinterpret_cast<uint4*>(ds_row + (((group * 4 + c) ^ (key & 7)) << 4)) =
+                make_uint4(packed[4 * c], packed[4 * c + 1], packed[4 * c + 2], packed[4 * c + 3]);
+          }
+          fence_proxy_async_smem();
         }
-        fence_proxy_async_smem();
         tc_fence_before();
-        mbar_arrive(&sm.ds_ready[group]);
+        mbar_arrive(&sm.ds_ready[set]);
       }
 
       // The next tile, and the loads it starts with, under this tile's epilogue.
@@ -460,7 +466,7 @@ __global__ void __launch_bounds__(kThreads, 1) fine_bwd_dq_kernel(const __grid_c
       const bool have_next =
           named_barrier_all(1, kMathThreads, tile_take(sm.tiles, seq + 1, next, abort_flag, p.status, 45));
       if (lane == 0) tile_release(sm.tiles, seq + 1);
-      if (have_next) fetch_rows_and_ids(next, ((g0 + pairs) ^ group) & 1);
+      if (have_next) fetch_rows_and_ids(next);
 
       // -------------------------------------------------------------- epilogue of the tile
       // Thread = head dim `key`; warpgroup g holds query rows [32g, 32g+32) of dQ^T.  The tile is
