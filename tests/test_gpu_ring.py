@@ -130,6 +130,32 @@ def test_ring_steps_replayed_on_one_gpu(name, size, partition, metadata_group):
         assert_close(dv_acc[rank][mine], fdv[rows], f"rank {rank} dv", peak_relative=True)
 
 
+def test_list_bounds_against_searchsorted():
+    """Range starts of ascending lists: rows of different length (empty and full included), ranges
+    without entries, a last range shorter than the others."""
+    gen = torch.Generator().manual_seed(5)
+    rows, capacity, blocks, chunk = 300, 90, 1000, 128
+    passes = -(-blocks // chunk)
+    counts = torch.randint(0, capacity + 1, (rows,), generator=gen, dtype=torch.int32)
+    counts[0], counts[1] = 0, capacity
+    lists = torch.zeros((rows, capacity), dtype=torch.int32)
+    for r in range(rows):
+        n = int(counts[r])
+        lists[r, :n] = torch.randperm(blocks, generator=gen)[:n].sort().values.int()
+    lists[2, :int(counts[2])] = torch.arange(int(counts[2]), dtype=torch.int32) + 3 * chunk  # one range only
+    bounds = torch.full((rows, passes + 1), -1, dtype=torch.int32, device="cuda")
+    p = _cabi.ptr
+    _cabi.call("vsa_list_bounds", p(lists.cuda()), p(counts.cuda()), rows, capacity, chunk, passes, p(bounds),
+               _cabi.stream())
+    want = torch.empty((rows, passes + 1), dtype=torch.int32)
+    edges = torch.arange(passes, dtype=torch.int32) * chunk
+    for r in range(rows):
+        n = int(counts[r])
+        want[r, :passes] = torch.searchsorted(lists[r, :n].contiguous(), edges)
+        want[r, passes] = n
+    assert torch.equal(bounds.cpu(), want)
+
+
 def test_partial_merge_with_empty_steps():
     torch.manual_seed(61)
     slots, heads = 129 * 1, 2
