@@ -277,16 +277,33 @@ class _VSAFunction(torch.autograd.Function):
                                              coarse.counts, (0, 0), coarse.kv_sizes, scale, plan.status)
             merge = (merge[0], coarse.block_q, gate, coarse_o, tokens)
         counts = layout.routing_counts
-        o_s, lse, out = _fine_fwd(q_s, k_s, v_s, index, counts, (index.stride(1), counts.stride(1)),
-                                  plan.sizes, scale, plan.status, merge=merge)
+        from . import vsa_ring  # the pass machinery of the ring steps (imported here: it imports this module)
+        bounds, passes = vsa_ring.list_bounds(index, counts, blocks)
+        if bounds is None:
+            o_s, lse, out = _fine_fwd(q_s, k_s, v_s, index, counts, (index.stride(1), counts.stride(1)),
+                                      plan.sizes, scale, plan.status, merge=merge)
+        else:
+            # K and V of one head do not fit L2: passes over KV ranges into a running FP32 output,
+            # exactly like the steps of a ring over one shard (vsa_ring.py).
+            out_f32 = torch.zeros((blocks * BLOCK, heads, dim), dtype=torch.float32, device=q.device)
+            lse = torch.full((heads, blocks * BLOCK), float("-inf"), dtype=torch.float32, device=q.device)
+            flat = bounds[0].flatten()
+            for c in range(passes):
+                _cabi.call("vsa_fine_fwd_running_range", _p(q_s), _p(k_s), _p(v_s), blocks, blocks, heads, _p(index),
+                           _p(flat[c:]), index.stride(1), counts.stride(1), passes + 1, index.shape[-1],
+                           _p(plan.sizes), scale, _p(out_f32), _p(lse), _p(plan.status), _cabi.stream())
+            o_s = torch.empty((blocks * BLOCK, heads, dim), dtype=q.dtype, device=q.device)
+            out = torch.empty((tokens, heads, dim), dtype=q.dtype, device=q.device)
+            _cabi.call("vsa_gate_merge", _p(out_f32), _p(merge[0]), _p(merge[1]), _p(merge[2]), _p(merge[3]), _p(o_s),
+                       _p(out), blocks, heads, tokens, _cabi.stream())
         ctx.save_for_backward(q_s, k_s, v_s, o_s, lse, index, gate if coarse is not None else None,
-                              tokens_bf16, coarse_o, coarse_lse)
-        ctx.layout, ctx.scale = layout, scale
+                              tokens_bf16, coarse_o, coarse_lse, bounds)
+        ctx.layout, ctx.scale, ctx.passes = layout, scale, passes
         return out
 
     @staticmethod
     def backward(ctx, grad):
-        q_s, k_s, v_s, o_s, lse, index, gate, tokens_bf16, coarse_o, coarse_lse = ctx.saved_tensors
+        q_s, k_s, v_s, o_s, lse, index, gate, tokens_bf16, coarse_o, coarse_lse, bounds = ctx.saved_tensors
         layout, scale = ctx.layout, ctx.scale
         plan = device_plan(layout)
         coarse = plan.coarse
@@ -312,12 +329,31 @@ class _VSAFunction(torch.autograd.Function):
                               coarse.counts, (0, 0), coarse.q_sizes, coarse.kv_sizes, scale, coarse_lse,
                               coarse_delta, plan.status)
         counts = layout.routing_counts
-        dq, dk, dv = _fine_bwd(q_s, k_s, v_s, grad_s, index, counts, (index.stride(1), counts.stride(1)),
-                               layout.block_sizes, plan.sizes, scale, lse, delta, plan.status,
-                               out_rows=(tokens, tokens), q_slot_row=slot_row, kv_slot_row=slot_row,
-                               pools=pools, q_block_coarse=coarse.block_q if coarse is not None else None,
-                               kv_block_coarse=coarse.block_q if coarse is not None else None)
-        return dq, dk, dv, dgate, None, None
+        if bounds is None:
+            dq, dk, dv = _fine_bwd(q_s, k_s, v_s, grad_s, index, counts, (index.stride(1), counts.stride(1)),
+                                   layout.block_sizes, plan.sizes, scale, lse, delta, plan.status,
+                                   out_rows=(tokens, tokens), q_slot_row=slot_row, kv_slot_row=slot_row,
+                                   pools=pools, q_block_coarse=coarse.block_q if coarse is not None else None,
+                                   kv_block_coarse=coarse.block_q if coarse is not None else None)
+            return dq, dk, dv, dgate, None, None
+        # Large layout: FP32 gradients in slot order, dQ in passes over KV ranges, dK / dV in passes
+        # over query-block ranges; pooled-mean terms, rounding and the row scatter at the end.
+        from . import vsa_ring
+        sums = torch.zeros((3, blocks * BLOCK, heads, dim), dtype=torch.float32, device=grad.device)
+        words = _cabi.load().vsa_kv_mask_words(blocks)
+        mask = torch.empty(heads * blocks * words, dtype=torch.int32, device=grad.device)
+        common = (q_s, k_s, v_s, grad_s, index[0], counts[0], layout.block_sizes, plan.sizes, scale, lse, delta, mask,
+                  plan.status)
+        vsa_ring._bwd_call(*common, parts=3, dq_f32=sums[0], accumulate=1, bounds=bounds[0], passes=ctx.passes)
+        vsa_ring._bwd_call(*common, parts=4, dk_f32=sums[1], dv_f32=sums[2], accumulate=1)
+        block_q = coarse.block_q if coarse is not None else None
+        grads = []
+        for acc, pool in zip(sums, pools if pools is not None else (None, None, None)):
+            out = torch.empty_like(grad)
+            _cabi.call("vsa_grad_finish", _p(acc), _p(slot_row), _p(pool), 0, _p(block_q) if pool is not None else None,
+                       _p(layout.block_sizes), _p(out), blocks, heads, tokens, _cabi.stream())
+            grads.append(out)
+        return grads[0], grads[1], grads[2], dgate, None, None
 
 
 def _field(mixed, n):

@@ -151,8 +151,9 @@ def partition(index, counts, layout, runtime):
 
 
 def _passes(blocks):
-    """Number of passes and blocks per pass for a range of `blocks` blocks."""
-    count = max(1, -(-blocks // RING_CHUNK_BLOCKS))
+    """Number of passes and blocks per pass for a range of `blocks` blocks (a range up to one and a
+    half times the pass size still runs in one pass)."""
+    count = max(1, int(blocks / RING_CHUNK_BLOCKS + 0.5))
     return count, -(-blocks // count)
 
 

@@ -202,6 +202,31 @@ def test_attention_against_fp32_oracle(name, order):
         assert_close(got.cpu(), ref, f"{name} {tag}", peak_relative=tag in ("dk", "dv"))
 
 
+@pytest.mark.parametrize("name,order,chunk", [("ragged", "raster", 8), ("c1", "block", 10), ("mixed", "raster", 3),
+                                              ("full_blocks", "block", 2), ("dense", "raster", 2)])
+def test_large_layout_passes_match_the_single_pass_path(name, order, chunk, monkeypatch):
+    """A layout with more blocks than one pass covers runs the fine attention in passes over KV
+    ranges (forward, dQ) and query-block ranges (dK/dV) into FP32 running results; forced here on
+    small geometries by a tiny pass size and compared with the one-pass path on the same inputs."""
+    from cudnn_vsa_b200 import vsa_ring
+    heads = 2
+    layout = build_vsa_layout(GEOMETRIES[name], head_num=heads, device="cuda", input_order=order)
+    q, k, v, gate = seeded(layout.tokens, heads, 0, 4)
+    dy, = seeded(layout.tokens, heads, 1, 1)
+    want_out, want_grads = _run(layout, q, k, v, gate, dy)
+    monkeypatch.setattr(vsa_ring, "RING_CHUNK_BLOCKS", chunk)
+    assert vsa_ring._passes(layout.blocks)[0] > 1
+    out, grads = _run(layout, q, k, v, gate, dy)
+    vsa_core.check_status(layout)
+    assert_close(out, want_out.float(), f"{name} out in passes", max_abs=8e-3, rel_l2=4e-3)
+    for tag, got, ref in zip(("dq", "dk", "dv", "dgate"), grads, want_grads):
+        if ref is None:
+            assert got is None
+            continue
+        assert_close(got, ref.float(), f"{name} {tag} in passes", max_abs=2e-2, rel_l2=6e-3,
+                     peak_relative=tag in ("dk", "dv"))
+
+
 @pytest.mark.parametrize("name", SMALL)
 def test_attention_against_reference_golden_vectors(name):
     """Output and gradients against the vectors of the reference's own CPU code.  Those carry the

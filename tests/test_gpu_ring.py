@@ -145,8 +145,8 @@ def test_list_bounds_against_searchsorted():
     lists[2, :int(counts[2])] = torch.arange(int(counts[2]), dtype=torch.int32) + 3 * chunk  # one range only
     bounds = torch.full((rows, passes + 1), -1, dtype=torch.int32, device="cuda")
     p = _cabi.ptr
-    _cabi.call("vsa_list_bounds", p(lists.cuda()), p(counts.cuda()), rows, capacity, chunk, passes, p(bounds),
-               _cabi.stream())
+    lists_d, counts_d = lists.cuda(), counts.cuda()
+    _cabi.call("vsa_list_bounds", p(lists_d), p(counts_d), rows, capacity, chunk, passes, p(bounds), _cabi.stream())
     want = torch.empty((rows, passes + 1), dtype=torch.int32)
     edges = torch.arange(passes, dtype=torch.int32) * chunk
     for r in range(rows):
@@ -179,8 +179,8 @@ def test_partial_merge_with_empty_steps():
 
 @pytest.mark.parametrize("chunk", [None, 16, 5])
 def test_size_one_ring_group_matches_single_device(chunk, monkeypatch):
-    """chunk: blocks per pass of a ring step (None = default, one pass here).  16 gives three KV
-    passes and two query-block passes of one mask word each on the 33 blocks; 5 gives seven."""
+    """chunk: blocks per pass of a ring step (None = default, one pass here).  16 gives two KV
+    passes and two query-block passes of one mask word each on the 33 blocks; 5 gives seven KV passes."""
     if chunk is not None:
         monkeypatch.setattr(vsa_ring, "RING_CHUNK_BLOCKS", chunk)
     if not dist.is_initialized():
