@@ -7,7 +7,10 @@
 // of the kernel.  A slot comes round again after kCounterSlots further launches of this process
 // on the device; launches that far apart are never in flight together (a stream or graph holds
 // a handful of these kernels at a time).  The memset is an ordinary stream operation and is
-// captured with the kernel when the launch is recorded into a CUDA graph.
+// captured with the kernel when the launch is recorded into a CUDA graph; a captured launch keeps
+// its slot for the life of the graph, so the one combination to avoid is replaying such a graph
+// on one stream while another stream of the same device issues its thousandth launch since the
+// capture at that very moment.
 #include <atomic>
 #include <mutex>
 
