@@ -35,8 +35,8 @@
 // from a work counter (the CTAs of the grid work on neighbouring query blocks of one head at a
 // time and share its K / V in L2; lists differ in length, so tiles are handed out as CTAs become
 // free rather than dealt in advance).  The thread that loads Q and K is the scheduler: it
-// publishes each tile's head, query block and list length in a small shared-memory queue that
-// the other roles read in order, one tile ahead of its own loads.  Barriers, tensor memory and the
+// publishes each tile's head, query block and list length (or list sub-range) in a small
+// shared-memory queue that the other roles read in order.  Barriers, tensor memory and the
 // stage / buffer rings are set up once and simply keep counting across tiles; Q has two buffers,
 // so the loads and the first S products of the next tile run under the last softmax rounds and the
 // epilogue of the current one.  Two hand-offs exist only between tiles: the S issuer releases a
