@@ -28,8 +28,7 @@ namespace {
 // sees 16-byte accesses of whole row segments: `term` is added, then BF16 rows go to the mapped
 // rows of `out` (row r, this head at out + row * out_row_stride + head_offset), or FP32 rows in
 // slot order to `out_f32` (added to the buffer's content when `accumulate`).  Padding slots are
-// left alone.  The FP32 read-modify-write fetches a batch of old values before it stores any, so
-// the loads are in flight together.  `release` (or null) gets one arrival per thread once the
+// left alone.  `release` (or null) gets one arrival per thread once the
 // accumulator has been read.
 __device__ __noinline__ void store_grad_tile(bool have_acc, uint32_t tmem_addr, float term, uint8_t* turn, int barrier_id, int t,
                                 const long long* out_rows, long long out_limit, __nv_bfloat16* out,
@@ -66,22 +65,16 @@ __device__ __noinline__ void store_grad_tile(bool have_acc, uint32_t tmem_addr, 
     float4* base = reinterpret_cast<float4*>(out_f32 + block * kBlock * width + head_col);
     const long long row_vecs = width / 4;
 #pragma unroll
-    for (int half = 0; half < 2; ++half) {
-      if (half * 32 >= valid) break;
-      float4 old[8];
-#pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        const int v = t + (half * 8 + j) * 128, r = v >> 5, c = v & 31;
-        old[j] = (accumulate && r < valid) ? base[r * row_vecs + c] : make_float4(0.f, 0.f, 0.f, 0.f);
-      }
-#pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        const int v = t + (half * 8 + j) * 128, r = v >> 5, c = v & 31;
-        if (r < valid) {
-          const float4 x = rows[v];
-          base[r * row_vecs + c] = make_float4(old[j].x + x.x, old[j].y + x.y, old[j].z + x.z, old[j].w + x.w);
-        }
-      }
+    for (int j = 0; j < 16; ++j) {
+      const int v = t + j * 128, r = v >> 5, c = v & 31;
+      if (r >= valid) break;
+      // Adding to a running sum is a vector reduction performed by the memory system: nothing is
+      // read back, so no load latency sits in the epilogue.  Every element has one writer per
+      // launch and launches are ordered by the stream, so the sum is the same as read-add-write.
+      if (accumulate)
+        atomicAdd(base + r * row_vecs + c, rows[v]);
+      else
+        base[r * row_vecs + c] = rows[v];
     }
   } else {
     const uint4* rows = reinterpret_cast<const uint4*>(turn);  // 16 vectors per row

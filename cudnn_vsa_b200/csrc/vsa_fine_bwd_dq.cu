@@ -514,25 +514,22 @@ __global__ void __launch_bounds__(kThreads, 1) fine_bwd_dq_kernel(const __grid_c
       const int math_tid = tid;  // 0..255
       if (add_nothing) {
       } else if (f32_out) {
-        // Running FP32 dQ of the ring: rows of 512 bytes, a float4 per thread and step; every old
-        // value is fetched before the first store, so the loads are in flight together.
+        // Running FP32 dQ of the ring: rows of 512 bytes, a float4 per thread and step.  Adding to
+        // the running sum is a vector reduction performed by the memory system: nothing is read
+        // back, so no load latency sits in the epilogue.  Every element has one writer per launch
+        // and launches are ordered by the stream, so the sum is the same as read-add-write.
         const float4* turn = reinterpret_cast<const float4*>(sm.ds[0]);
         float4* base = reinterpret_cast<float4*>(p.dq_f32 + static_cast<long long>(qb) * kBlock * width +
                                                  static_cast<long long>(head) * kDim);
         const long long row_vecs = width / 4;
-        float4 old[8];
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
           const int v = math_tid + j * kMathThreads, r = v >> 5, c = v & 31;
-          old[j] = (p.f32_accumulate && r < q_size) ? base[r * row_vecs + c] : make_float4(0.f, 0.f, 0.f, 0.f);
-        }
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          const int v = math_tid + j * kMathThreads, r = v >> 5, c = v & 31;
-          if (r < q_size) {
-            const float4 x = turn[v];
-            base[r * row_vecs + c] = make_float4(old[j].x + x.x, old[j].y + x.y, old[j].z + x.z, old[j].w + x.w);
-          }
+          if (r >= q_size) break;
+          if (p.f32_accumulate)
+            atomicAdd(base + r * row_vecs + c, turn[v]);
+          else
+            base[r * row_vecs + c] = turn[v];
         }
       } else {
         const uint4* turn = reinterpret_cast<const uint4*>(sm.ds[0]);
