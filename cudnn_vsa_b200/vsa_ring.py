@@ -190,7 +190,8 @@ def _bwd_call(q, k, v, d_o, index, counts, sizes_q, sizes_kv, scale, lse, delta,
     words = _cabi.load().vsa_kv_mask_words(q_blocks)
     q_passes, _ = _passes(q_blocks)
     with _cabi.mark("ring_step_dq" if parts & 2 else "ring_step_dkv"):
-        if parts & 2 and bounds is None or parts & 4 and q_passes == 1:
+        one_pass = bounds is None if parts & 2 else q_passes == 1
+        if one_pass:
             _bwd_launch(q, k, v, d_o, index, counts, sizes_q, sizes_kv, scale, lse, delta, mask, status, parts | hint,
                         dq, dk, dv, dq_f32, dk_f32, dv_f32, accumulate, heads, q_blocks, kv_blocks)
             return
