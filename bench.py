@@ -543,14 +543,18 @@ def main():
         # Host buffers are pinned; the device side is a prefetching loader: two sets of input
         # buffers, uploads on a copy stream (the next step's inputs travel while this step
         # computes), downloads of the output and the gradients on another (they drain under
-        # the next step).  Every step's copies and the final drain are inside the timed region.
+        # the next step).  The forward pass starts as soon as its four inputs are up (dO follows
+        # under it) and the output goes down while the backward pass runs.  Every step's copies
+        # and the final drain are inside the timed region.
         host_in = [x.detach().cpu().pin_memory() for x in (*leaves, dy)]
         host_out = [torch.empty_like(h).pin_memory() for h in host_in]
         dev_in = [[torch.empty_like(x) for x in (*leaves, dy)] for _ in range(2)]
         main_stream = torch.cuda.current_stream()
         up, down = torch.cuda.Stream(), torch.cuda.Stream()
         uploaded = [torch.cuda.Event() for _ in range(2)]
+        uploaded_inputs = [torch.cuda.Event() for _ in range(2)]
         consumed = [torch.cuda.Event() for _ in range(2)]
+        forward_done = torch.cuda.Event()
         inputs = len(leaves)
 
         def upload(step_no):
@@ -558,8 +562,10 @@ def main():
             with torch.cuda.stream(up):
                 if step_no >= 2:
                     up.wait_event(consumed[buf])  # the step that last used these buffers has finished
-                for d, h in zip(dev_in[buf], host_in):
+                for i, (d, h) in enumerate(zip(dev_in[buf], host_in)):
                     d.copy_(h, non_blocking=True)
+                    if i + 1 == inputs:
+                        uploaded_inputs[buf].record(up)
                 uploaded[buf].record(up)
 
         def e2e_run(steps):
@@ -571,16 +577,22 @@ def main():
                 buf = step_no & 1
                 if step_no + 1 < steps:
                     upload(step_no + 1)
-                main_stream.wait_event(uploaded[buf])
+                main_stream.wait_event(uploaded_inputs[buf])
                 xs = [d.requires_grad_() for d in dev_in[buf][:inputs]]
                 out = forward(xs)
-                results = (out, *torch.autograd.grad(out, xs, dev_in[buf][inputs]))
+                forward_done.record(main_stream)
+                with torch.cuda.stream(down):
+                    down.wait_event(forward_done)
+                    out.record_stream(down)
+                    host_out[0].copy_(out.detach(), non_blocking=True)
+                main_stream.wait_event(uploaded[buf])
+                grads = torch.autograd.grad(out, xs, dev_in[buf][inputs])
                 consumed[buf].record(main_stream)
                 for d in dev_in[buf]:
                     d.requires_grad_(False)
                 down.wait_stream(main_stream)
                 with torch.cuda.stream(down):
-                    for h, r in zip(host_out, results):
+                    for h, r in zip(host_out[1:], grads):
                         r.record_stream(down)
                         h.copy_(r, non_blocking=True)
             main_stream.wait_stream(down)
