@@ -528,7 +528,7 @@ def main():
         name = max(kernels, key=lambda n: kernels[n]["ms"])
         top = kernels[name]
         # DRAM bytes per listed block pair from the ncu captures of the 6-head single sample
-        # (profiles/<kernel>_720p_single_sample_h6.md: dram read + write over 2,623,488 pairs),
+        # (the per-kernel summaries under profiles/: dram read + write over 2,623,488 pairs),
         # scaled to this workload by its number of listed pairs (traffic grows with the tiles).
         per_pair = {"fine_fwd_kernel": 1480.4, "fine_bwd_dq_kernel": 1533.0, "fine_bwd_dkv_kernel": 2199.3}
         listed = float(layout.routing_counts.sum().item())
