@@ -98,3 +98,14 @@ def test_ring_coarse_plan_streams(metadata_group):
         assert torch.equal(coarse.kv_src[coarse.kv_src >= 0], layout.coarse_kv_blocks)
         assert coarse.q_rows % 64 == 0 and coarse.kv_rows % 64 == 0
         assert int(coarse.kv_sizes.sum()) == layout.coarse_kv_blocks.numel()
+
+
+def test_pass_counts_for_the_benchmark_shards():
+    """Blocks per pass: a range up to one and a half pass sizes runs in one pass; the ring
+    configuration's shards (1848 / 3696 / 7392 blocks at 8 / 4 / 2 ranks) and the whole geometry
+    (14784) run in 1 / 2 / 4 / 7 passes; every pass fits the pass size plus its rounding."""
+    assert vsa_ring.RING_CHUNK_BLOCKS == 2048
+    for blocks, want in ((1, 1), (1848, 1), (3000, 1), (3072, 2), (3696, 2), (7392, 4), (14784, 7)):
+        passes, per = vsa_ring._passes(blocks)
+        assert passes == want and (passes - 1) * per < blocks <= passes * per
+        assert per <= 1.5 * vsa_ring.RING_CHUNK_BLOCKS
